@@ -1,0 +1,174 @@
+/* Internal declarations shared by the translation units of libh3b200.so. */
+#pragma once
+
+#include "../../include/h3b200.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+/* The first five members keep the order the reference's CUDA tensor has
+ * (h3_cuda_internal.h:20-26): one reference test builds offset views by
+ * re-declaring that struct (tests/test_cuda_core.c:749-763). */
+struct h3_gpu_tensor {
+    void *data;
+    size_t elements;
+    size_t bytes;
+    h3_gpu_dtype dtype;
+    struct h3_gpu *owner;
+    int external;  /* wraps caller-owned memory: never freed or cached */
+};
+
+/* Device-side status word written by kernels whose bounded waits expire. */
+enum : int {
+    H3B_STATUS_OK = 0,
+    H3B_STATUS_GEMM_TIMEOUT = 1,
+    H3B_STATUS_ATTN_TIMEOUT = 2,
+};
+
+struct h3b_pinned_slot {
+    void *host = nullptr;
+    size_t bytes = 0;
+    cudaEvent_t done = nullptr;
+    bool pending = false;
+};
+
+struct h3_gpu {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;  /* nullptr = legacy default stream */
+    int active = 0;                 /* between begin and submit */
+    char error[512] = {0};
+    h3_gpu_stats stats = {};
+    double command_start = 0.0;
+
+    /* grow-only scratch for intermediates of composite ops (MLP, final head) */
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+
+    /* exact-size cache of freed device blocks; reuse is ordered by the stream */
+    std::unordered_multimap<size_t, void *> cache;
+    size_t cache_bytes = 0;
+    size_t cache_limit = 0;
+
+    /* pinned staging ring for host -> device writes */
+    static constexpr int kSlots = 4;
+    static constexpr size_t kSlotMax = size_t(32) << 20;
+    h3b_pinned_slot slots[kSlots];
+    unsigned next_slot = 0;
+
+    int *status_device = nullptr;   /* kernel status word */
+    int status_seen = 0;
+
+    /* block-sparse attention mask registration (kept for API parity) */
+    uint32_t sparse_rows = 0;
+
+    char profile_label[128] = {0};
+    double profile_mark = 0.0;
+    std::mutex io_mutex;            /* file streaming may run on another thread */
+};
+
+double h3b_now();
+
+inline size_t h3b_item_size(h3_gpu_dtype dtype) {
+    return dtype == H3_GPU_BF16 ? 2 : dtype == H3_GPU_I8 ? 1 : 4;
+}
+
+inline int h3b_fail(h3_gpu *gpu, const char *format, ...) {
+    if (gpu) {
+        va_list args;
+        va_start(args, format);
+        vsnprintf(gpu->error, sizeof(gpu->error), format, args);
+        va_end(args);
+    }
+    return 0;
+}
+
+inline int h3b_fail_cuda(h3_gpu *gpu, const char *what, cudaError_t status) {
+    return h3b_fail(gpu, "CUDA %s failed: %s", what, cudaGetErrorString(status));
+}
+
+/* Which statistics counter a launch belongs to (reference h3_cuda_internal.h:142-156). */
+enum h3b_kind { H3B_DIRECT = 0, H3B_LINEAR = 1, H3B_CONV = 2, H3B_SDPA = 3 };
+
+inline int h3b_launched(h3_gpu *gpu, const char *what, h3b_kind kind = H3B_DIRECT) {
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return h3b_fail_cuda(gpu, what, status);
+    switch (kind) {
+        case H3B_LINEAR: gpu->stats.mps_linear_dispatches++; break;
+        case H3B_CONV: gpu->stats.mps_conv_dispatches++; break;
+        case H3B_SDPA: gpu->stats.mps_sdpa_dispatches++; break;
+        default: gpu->stats.direct_dispatches++; break;
+    }
+    return 1;
+}
+
+inline int h3b_need_command(h3_gpu *gpu) {
+    if (!gpu || !gpu->active) return h3b_fail(gpu, "no active command buffer");
+    return 1;
+}
+
+inline int h3b_need(h3_gpu *gpu, const h3_gpu_tensor *t, h3_gpu_dtype dtype, size_t elements,
+                    const char *label) {
+    if (!t || t->dtype != dtype) return h3b_fail(gpu, "%s tensor has the wrong dtype", label);
+    if (t->elements < elements) return h3b_fail(gpu, "%s tensor is too small", label);
+    return 1;
+}
+
+void *h3b_workspace(h3_gpu *gpu, size_t bytes);
+
+template <class T>
+inline T *h3b_ptr(const h3_gpu_tensor *t, size_t offset = 0) {
+    return reinterpret_cast<T *>(t->data) + offset;
+}
+
+inline bool h3b_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+/* ---- device helpers --------------------------------------------------- */
+#ifdef __CUDACC__
+__device__ __forceinline__ float h3b_widen(uint16_t v) {
+    return __uint_as_float(static_cast<uint32_t>(v) << 16);
+}
+/* round to nearest even with the reference's integer formula */
+__device__ __forceinline__ uint16_t h3b_narrow(float v) {
+    uint32_t bits = __float_as_uint(v);
+    bits += 0x7fffu + ((bits >> 16) & 1u);
+    return static_cast<uint16_t>(bits >> 16);
+}
+__device__ __forceinline__ uint32_t h3b_narrow2(float lo, float hi) {
+    return static_cast<uint32_t>(h3b_narrow(lo)) | (static_cast<uint32_t>(h3b_narrow(hi)) << 16);
+}
+__device__ __forceinline__ float h3b_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float h3b_hi(uint32_t packed) {
+    return __uint_as_float(packed & 0xffff0000u);
+}
+__device__ __forceinline__ float h3b_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+#endif
+
+/* ---- cross-unit entry points ------------------------------------------ */
+/* C[rows,n] = X[rows,k] . W[n,k]^T (+bias) with BF16 in/out and F32 accumulate.
+ * Picks the tcgen05 kernel when the shape allows it, else the SIMT kernel. */
+enum h3b_gemm_epilogue {
+    H3B_EPI_STORE = 0,    /* out[r][c] = bf16(acc + bias[c])                          */
+    H3B_EPI_SWIGLU = 1,   /* W = [gate rows | up rows]; out[r][c] = swiglu, n = hidden */
+};
+int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
+                  const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t n,
+                  h3b_gemm_epilogue epilogue, const char *what);
+int h3b_swiglu_launch(h3_gpu *gpu, uint16_t *out, const uint16_t *fused, uint32_t rows,
+                      uint32_t width);
+int h3b_qkv_rope_launch(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const uint16_t *qkv,
+                        const uint16_t *qn, const uint16_t *kn, const uint16_t *rc,
+                        const uint16_t *rs, uint32_t seq, uint32_t heads, uint32_t hd,
+                        uint32_t rope_half, int grouped, float eps);
+bool h3b_tensor_map_available();

@@ -1,0 +1,643 @@
+/* Context, tensors, host<->device traffic, command bracketing, casts and copies
+ * of libh3b200.so. Replaces the reference's h3_gpu_cuda.cu behind the same C ABI.
+ *
+ * Design notes
+ *  - One in-order stream per context. By default it is the legacy default
+ *    stream, as in the reference, so a host process that also uses another
+ *    CUDA library on that stream stays ordered with us; h3x_set_stream()
+ *    moves the context to a caller-owned stream (one process per GPU).
+ *  - Freed device blocks go to an exact-size cache and are handed out again
+ *    without synchronising: reuse is ordered by the stream.
+ *  - Host writes go through a small ring of pinned buffers so that the call
+ *    can return as soon as the host buffer has been consumed.
+ */
+#include "h3b_common.cuh"
+
+#include <cerrno>
+#include <cstdlib>
+#include <ctime>
+#include <fcntl.h>
+#include <unistd.h>
+
+static thread_local int g_device = 0;
+
+double h3b_now() {
+    timespec t;
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    return double(t.tv_sec) + double(t.tv_nsec) * 1e-9;
+}
+
+/* ------------------------------------------------------------ allocator */
+
+static void cache_evict_all(h3_gpu *gpu) {
+    for (auto &entry : gpu->cache) cudaFree(entry.second);
+    gpu->cache.clear();
+    gpu->cache_bytes = 0;
+}
+
+static cudaError_t cache_alloc(h3_gpu *gpu, size_t bytes, void **out) {
+    auto hit = gpu->cache.find(bytes);
+    if (hit != gpu->cache.end()) {
+        *out = hit->second;
+        gpu->cache.erase(hit);
+        gpu->cache_bytes -= bytes;
+        return cudaSuccess;
+    }
+    if (gpu->cache_bytes > gpu->cache_limit) {
+        cudaStreamSynchronize(gpu->stream);
+        cache_evict_all(gpu);
+    }
+    cudaError_t status = cudaMalloc(out, bytes);
+    if (status != cudaSuccess && !gpu->cache.empty()) {
+        cudaGetLastError();
+        cudaStreamSynchronize(gpu->stream);
+        cache_evict_all(gpu);
+        status = cudaMalloc(out, bytes);
+    }
+    return status;
+}
+
+static void cache_release(h3_gpu *gpu, void *data, size_t bytes) {
+    gpu->cache.emplace(bytes, data);
+    gpu->cache_bytes += bytes;
+}
+
+void *h3b_workspace(h3_gpu *gpu, size_t bytes) {
+    if (!bytes) bytes = 1;
+    if (gpu->workspace && bytes <= gpu->workspace_bytes) return gpu->workspace;
+    size_t capacity = gpu->workspace_bytes ? gpu->workspace_bytes : (size_t(1) << 20);
+    while (capacity < bytes) capacity = capacity > SIZE_MAX / 2 ? bytes : capacity * 2;
+    void *fresh = nullptr;
+    if (cudaMalloc(&fresh, capacity) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    cudaStreamSynchronize(gpu->stream);  /* kernels in flight may still use the old block */
+    cudaFree(gpu->workspace);
+    gpu->workspace = fresh;
+    gpu->workspace_bytes = capacity;
+    return fresh;
+}
+
+/* ----------------------------------------------------------- host I/O */
+
+static bool upload(h3_gpu *gpu, void *device, const void *host, size_t bytes) {
+    if (!bytes) return true;
+    const unsigned char *src = static_cast<const unsigned char *>(host);
+    unsigned char *dst = static_cast<unsigned char *>(device);
+    while (bytes) {
+        size_t chunk = bytes < h3_gpu::kSlotMax ? bytes : h3_gpu::kSlotMax;
+        h3b_pinned_slot &slot = gpu->slots[gpu->next_slot++ % h3_gpu::kSlots];
+        if (slot.pending) {
+            if (cudaEventSynchronize(slot.done) != cudaSuccess) return false;
+            slot.pending = false;
+        }
+        if (slot.bytes < chunk) {
+            if (slot.host) cudaFreeHost(slot.host);
+            slot.host = nullptr;
+            slot.bytes = 0;
+            size_t want = chunk < (size_t(1) << 16) ? (size_t(1) << 16) : chunk;
+            if (cudaMallocHost(&slot.host, want) != cudaSuccess) {
+                cudaGetLastError();
+                /* no pinned memory: a pageable copy is staged by the runtime before it returns */
+                if (cudaMemcpyAsync(dst, src, chunk, cudaMemcpyHostToDevice, gpu->stream) !=
+                    cudaSuccess)
+                    return false;
+                src += chunk; dst += chunk; bytes -= chunk;
+                continue;
+            }
+            slot.bytes = want;
+        }
+        if (!slot.done && cudaEventCreateWithFlags(&slot.done, cudaEventDisableTiming) != cudaSuccess)
+            return false;
+        memcpy(slot.host, src, chunk);
+        if (cudaMemcpyAsync(dst, slot.host, chunk, cudaMemcpyHostToDevice, gpu->stream) !=
+                cudaSuccess ||
+            cudaEventRecord(slot.done, gpu->stream) != cudaSuccess)
+            return false;
+        slot.pending = true;
+        src += chunk; dst += chunk; bytes -= chunk;
+    }
+    return true;
+}
+
+static bool download(const h3_gpu *gpu, void *host, const void *device, size_t bytes) {
+    if (!bytes) return true;
+    cudaStream_t stream = gpu ? gpu->stream : nullptr;
+    if (cudaMemcpyAsync(host, device, bytes, cudaMemcpyDeviceToHost, stream) != cudaSuccess)
+        return false;
+    return cudaStreamSynchronize(stream) == cudaSuccess;
+}
+
+/* -------------------------------------------------------------- context */
+
+extern "C" int h3x_set_device(int device) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return 0;
+    }
+    g_device = device;
+    return cudaSetDevice(device) == cudaSuccess;
+}
+
+extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
+    auto fail = [&](const char *what, cudaError_t status) -> h3_gpu * {
+        if (error && error_size)
+            snprintf(error, error_size, "%s: %s", what, cudaGetErrorString(status));
+        cudaGetLastError();
+        return nullptr;
+    };
+    int count = 0;
+    cudaError_t status = cudaGetDeviceCount(&count);
+    if (status != cudaSuccess || count <= 0) {
+        if (error && error_size) snprintf(error, error_size, "no CUDA device available");
+        cudaGetLastError();
+        return nullptr;
+    }
+    status = cudaSetDevice(g_device);
+    if (status == cudaSuccess) status = cudaFree(nullptr);
+    if (status != cudaSuccess) return fail("cannot initialize CUDA device", status);
+    cudaDeviceProp prop;
+    status = cudaGetDeviceProperties(&prop, g_device);
+    if (status != cudaSuccess) return fail("cannot query CUDA device", status);
+    if (prop.major != 10) {
+        if (error && error_size)
+            snprintf(error, error_size,
+                     "libh3b200 needs an sm_100 (B200) device; device %d is sm_%d%d", g_device,
+                     prop.major, prop.minor);
+        return nullptr;
+    }
+    h3_gpu *gpu = new (std::nothrow) h3_gpu();
+    if (!gpu) {
+        if (error && error_size) snprintf(error, error_size, "out of memory");
+        return nullptr;
+    }
+    gpu->device = g_device;
+    gpu->sm_count = prop.multiProcessorCount;
+    size_t available = 0, total = 0;
+    if (cudaMemGetInfo(&available, &total) == cudaSuccess) gpu->cache_limit = total / 5;
+    status = cudaMalloc(reinterpret_cast<void **>(&gpu->status_device), sizeof(int));
+    if (status == cudaSuccess) status = cudaMemset(gpu->status_device, 0, sizeof(int));
+    if (status != cudaSuccess) {
+        delete gpu;
+        return fail("cannot allocate the kernel status word", status);
+    }
+    gpu->profile_mark = h3b_now();
+    return gpu;
+}
+
+extern "C" void h3_gpu_free(h3_gpu *gpu) {
+    if (!gpu) return;
+    cudaSetDevice(gpu->device);
+    cudaStreamSynchronize(gpu->stream);
+    if (gpu->workspace) cudaFree(gpu->workspace);
+    cache_evict_all(gpu);
+    for (h3b_pinned_slot &slot : gpu->slots) {
+        if (slot.host) cudaFreeHost(slot.host);
+        if (slot.done) cudaEventDestroy(slot.done);
+    }
+    if (gpu->status_device) cudaFree(gpu->status_device);
+    delete gpu;
+}
+
+extern "C" int h3_gpu_is_m5(const h3_gpu *) { return 0; }
+extern "C" int h3_gpu_has_nax_mlp(const h3_gpu *) { return 0; }
+extern "C" int h3_gpu_has_int8_mlp(const h3_gpu *) { return 0; }
+extern "C" int h3_gpu_prefers_gpu_sampler(const h3_gpu *) { return 1; }
+
+extern "C" int h3x_set_stream(h3_gpu *gpu, void *cuda_stream) {
+    if (!gpu) return 0;
+    if (gpu->active) return h3b_fail(gpu, "cannot change the stream inside a command");
+    cudaStreamSynchronize(gpu->stream);
+    gpu->stream = static_cast<cudaStream_t>(cuda_stream);
+    return 1;
+}
+
+extern "C" int h3x_kernel_status(h3_gpu *gpu) {
+    if (!gpu) return -1;
+    int status = 0;
+    if (!download(gpu, &status, gpu->status_device, sizeof(int))) return -1;
+    return status;
+}
+
+extern "C" int h3_gpu_begin(h3_gpu *gpu) {
+    if (!gpu || gpu->active) return 0;
+    gpu->error[0] = '\0';
+    gpu->active = 1;
+    gpu->command_start = h3b_now();
+    return 1;
+}
+
+extern "C" int h3_gpu_continue(h3_gpu *gpu) {
+    if (!gpu || !gpu->active) return 0;
+    double now = h3b_now();
+    gpu->stats.submissions++;
+    gpu->stats.command_encode_seconds += now - gpu->command_start;
+    gpu->command_start = now;
+    return 1;
+}
+
+extern "C" int h3_gpu_submit(h3_gpu *gpu) {
+    if (!gpu || !gpu->active) return 0;
+    gpu->active = 0;
+    double committed = h3b_now();
+    int kernel_status = 0;
+    /* one small read-back both waits for the stream and fetches the status word */
+    cudaError_t status = cudaMemcpyAsync(&kernel_status, gpu->status_device, sizeof(int),
+                                         cudaMemcpyDeviceToHost, gpu->stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(gpu->stream);
+    double completed = h3b_now();
+    gpu->stats.submissions++;
+    gpu->stats.command_encode_seconds += committed - gpu->command_start;
+    gpu->stats.command_wait_seconds += completed - committed;
+    gpu->stats.gpu_seconds += completed - committed;
+    if (status != cudaSuccess) return h3b_fail_cuda(gpu, "command execution", status);
+    if (kernel_status != H3B_STATUS_OK) {
+        cudaMemsetAsync(gpu->status_device, 0, sizeof(int), gpu->stream);
+        gpu->status_seen = kernel_status;
+        return h3b_fail(gpu, "a %s kernel gave up waiting on its pipeline (status %d)",
+                        kernel_status == H3B_STATUS_GEMM_TIMEOUT ? "GEMM" : "attention",
+                        kernel_status);
+    }
+    return 1;
+}
+
+extern "C" const char *h3_gpu_error(const h3_gpu *gpu) {
+    if (!gpu || !gpu->error[0]) return "unknown CUDA error";
+    return gpu->error;
+}
+
+extern "C" int h3_gpu_get_stats(const h3_gpu *gpu, h3_gpu_stats *stats) {
+    if (!gpu || !stats) return 0;
+    *stats = gpu->stats;
+    return 1;
+}
+
+extern "C" void h3_gpu_profile_set_label(h3_gpu *gpu, const char *label) {
+    if (!gpu || !label || !*label) return;
+    snprintf(gpu->profile_label, sizeof(gpu->profile_label), "%s", label);
+}
+
+extern "C" void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase) {
+    if (!gpu || !phase || !*phase) return;
+    const char *enabled = getenv("H3_PROFILE");
+    if (!enabled || !*enabled || !strcmp(enabled, "0")) return;
+    double now = h3b_now();
+    fprintf(stderr, "h3b200: [%s] %s: %.3f s wall, %.3f s waiting, %llu kernels, %llu GEMMs, %llu attention\n",
+            gpu->profile_label[0] ? gpu->profile_label : "gpu", phase, now - gpu->profile_mark,
+            gpu->stats.command_wait_seconds,
+            (unsigned long long)gpu->stats.direct_dispatches,
+            (unsigned long long)gpu->stats.mps_linear_dispatches,
+            (unsigned long long)gpu->stats.mps_sdpa_dispatches);
+    gpu->profile_mark = now;
+}
+
+extern "C" int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t, const uint32_t *,
+                                      size_t, uint32_t) {
+    if (!gpu) return 0;
+    if (!ptr) {
+        gpu->sparse_rows = 0;
+        return 1;
+    }
+    return h3b_fail(gpu, "block-sparse attention masks are not supported by this backend");
+}
+
+/* -------------------------------------------------------------- tensors */
+
+static h3_gpu_tensor *tensor_new(h3_gpu *gpu, const void *values, size_t elements,
+                                 h3_gpu_dtype dtype) {
+    size_t item = h3b_item_size(dtype);
+    if (!gpu || elements > SIZE_MAX / item) return nullptr;
+    size_t bytes = elements * item;
+    h3_gpu_tensor *tensor = new (std::nothrow) h3_gpu_tensor();
+    if (!tensor) {
+        h3b_fail(gpu, "out of memory");
+        return nullptr;
+    }
+    cudaSetDevice(gpu->device);
+    /* round the block up so that vector loads past an odd tail stay inside it */
+    size_t block = ((bytes ? bytes : 1) + 255) & ~size_t(255);
+    cudaError_t status = cache_alloc(gpu, block, &tensor->data);
+    if (status != cudaSuccess) {
+        cudaGetLastError();
+        h3b_fail_cuda(gpu, "tensor allocation", status);
+        delete tensor;
+        return nullptr;
+    }
+    tensor->elements = elements;
+    tensor->bytes = bytes;
+    tensor->dtype = dtype;
+    tensor->owner = gpu;
+    tensor->external = 0;
+    if (values && bytes && !upload(gpu, tensor->data, values, bytes)) {
+        h3b_fail(gpu, "tensor upload failed");
+        cache_release(gpu, tensor->data, block);
+        delete tensor;
+        return nullptr;
+    }
+    gpu->stats.allocated_bytes += bytes;
+    gpu->stats.live_bytes += bytes;
+    if (gpu->stats.live_bytes > gpu->stats.peak_live_bytes)
+        gpu->stats.peak_live_bytes = gpu->stats.live_bytes;
+    gpu->stats.tensor_allocations++;
+    return tensor;
+}
+
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *gpu, size_t n) {
+    return tensor_new(gpu, nullptr, n, H3_GPU_F32);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *gpu, size_t n) {
+    return tensor_new(gpu, nullptr, n, H3_GPU_BF16);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_i8(h3_gpu *gpu, size_t n) {
+    return tensor_new(gpu, nullptr, n, H3_GPU_I8);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *gpu, const float *v, size_t n) {
+    return tensor_new(gpu, v, n, H3_GPU_F32);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *gpu, const uint16_t *v, size_t n) {
+    return tensor_new(gpu, v, n, H3_GPU_BF16);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *gpu, const uint32_t *v, size_t n) {
+    return tensor_new(gpu, v, n, H3_GPU_U32);
+}
+
+extern "C" h3_gpu_tensor *h3x_tensor_wrap(h3_gpu *gpu, void *device_pointer, size_t elements,
+                                          h3_gpu_dtype dtype) {
+    if (!gpu || (!device_pointer && elements)) return nullptr;
+    h3_gpu_tensor *tensor = new (std::nothrow) h3_gpu_tensor();
+    if (!tensor) return nullptr;
+    tensor->data = device_pointer;
+    tensor->elements = elements;
+    tensor->bytes = elements * h3b_item_size(dtype);
+    tensor->dtype = dtype;
+    tensor->owner = gpu;
+    tensor->external = 1;
+    return tensor;
+}
+
+extern "C" void *h3x_tensor_device_pointer(const h3_gpu_tensor *tensor) {
+    return tensor ? tensor->data : nullptr;
+}
+
+extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *tensor) {
+    if (!tensor) return;
+    h3_gpu *owner = tensor->owner;
+    if (!tensor->external) {
+        if (owner)
+            owner->stats.live_bytes =
+                owner->stats.live_bytes >= tensor->bytes ? owner->stats.live_bytes - tensor->bytes : 0;
+        if (tensor->data) {
+            size_t block = ((tensor->bytes ? tensor->bytes : 1) + 255) & ~size_t(255);
+            if (owner) cache_release(owner, tensor->data, block);
+            else cudaFree(tensor->data);
+        }
+    }
+    delete tensor;
+}
+
+extern "C" size_t h3_gpu_tensor_elements(const h3_gpu_tensor *t) { return t ? t->elements : 0; }
+extern "C" h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *t) {
+    return t ? t->dtype : H3_GPU_F32;
+}
+
+static int read_range(const h3_gpu_tensor *t, h3_gpu_dtype dtype, size_t offset, void *values,
+                      size_t elements) {
+    if (!t || !values || t->dtype != dtype || offset > t->elements ||
+        elements > t->elements - offset)
+        return 0;
+    size_t item = h3b_item_size(dtype);
+    return download(t->owner, values, static_cast<const unsigned char *>(t->data) + offset * item,
+                    elements * item);
+}
+
+static int write_range(h3_gpu_tensor *t, h3_gpu_dtype dtype, size_t offset, const void *values,
+                       size_t elements) {
+    if (!t || !values || !t->owner || t->dtype != dtype || offset > t->elements ||
+        elements > t->elements - offset)
+        return 0;
+    size_t item = h3b_item_size(dtype);
+    return upload(t->owner, static_cast<unsigned char *>(t->data) + offset * item, values,
+                  elements * item);
+}
+
+extern "C" int h3_gpu_tensor_read_f32(const h3_gpu_tensor *t, float *v, size_t n) {
+    return read_range(t, H3_GPU_F32, 0, v, n);
+}
+extern "C" int h3_gpu_tensor_read_f32_range(const h3_gpu_tensor *t, size_t o, float *v, size_t n) {
+    return read_range(t, H3_GPU_F32, o, v, n);
+}
+extern "C" int h3_gpu_tensor_read_bf16(const h3_gpu_tensor *t, uint16_t *v, size_t n) {
+    return read_range(t, H3_GPU_BF16, 0, v, n);
+}
+extern "C" int h3_gpu_tensor_write_f32(h3_gpu_tensor *t, const float *v, size_t n) {
+    return write_range(t, H3_GPU_F32, 0, v, n);
+}
+extern "C" int h3_gpu_tensor_write_f32_range(h3_gpu_tensor *t, size_t o, const float *v, size_t n) {
+    return write_range(t, H3_GPU_F32, o, v, n);
+}
+extern "C" int h3_gpu_tensor_write_bf16(h3_gpu_tensor *t, const uint16_t *v, size_t n) {
+    return write_range(t, H3_GPU_BF16, 0, v, n);
+}
+extern "C" int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *t, size_t o, const uint16_t *v,
+                                              size_t n) {
+    return write_range(t, H3_GPU_BF16, o, v, n);
+}
+
+/* ------------------------------------------------------------ file loads */
+/* Payload bytes are read with pread() into a pinned bounce buffer, 16 MiB at a
+ * time on two alternating buffers, and copied to the device on a private
+ * stream, so a load may run on an I/O thread while the main thread keeps
+ * issuing kernels on tensors that are not being filled. */
+
+static int fill_from_file(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
+                          size_t elements, h3_gpu_dtype dtype, char *error, size_t error_size) {
+    auto fail = [&](const char *what) {
+        if (error && error_size) snprintf(error, error_size, "%s: %s", what, path ? path : "(null)");
+        return 0;
+    };
+    if (!tensor || !path || tensor->dtype != dtype || elements > tensor->elements)
+        return fail("invalid tensor file read");
+    size_t bytes = elements * h3b_item_size(dtype);
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail("cannot open tensor file");
+    h3_gpu *gpu = tensor->owner;
+    if (gpu) cudaSetDevice(gpu->device);
+    const size_t chunk = size_t(16) << 20;
+    void *bounce[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaStream_t stream = nullptr;
+    int ok = 1;
+    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) ok = 0;
+    for (int i = 0; ok && i < 2; i++)
+        if (cudaMallocHost(&bounce[i], chunk) != cudaSuccess ||
+            cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) != cudaSuccess)
+            ok = 0;
+    if (!ok) fail("cannot allocate staging memory for");
+    size_t moved = 0;
+    for (int turn = 0; ok && moved < bytes; turn ^= 1) {
+        size_t want = bytes - moved < chunk ? bytes - moved : chunk;
+        if (cudaEventSynchronize(done[turn]) != cudaSuccess) { ok = fail("staging wait failed for"); break; }
+        size_t got = 0;
+        while (got < want) {
+            ssize_t n = pread(fd, static_cast<char *>(bounce[turn]) + got, want - got,
+                              off_t(file_offset + moved + got));
+            if (n < 0 && errno == EINTR) continue;
+            if (n <= 0) break;
+            got += size_t(n);
+        }
+        if (got != want) { ok = fail("short read from"); break; }
+        if (cudaMemcpyAsync(static_cast<char *>(tensor->data) + moved, bounce[turn], want,
+                            cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+            cudaEventRecord(done[turn], stream) != cudaSuccess) {
+            ok = fail("device upload failed for");
+            break;
+        }
+        moved += want;
+    }
+    if (stream) cudaStreamSynchronize(stream);
+    for (int i = 0; i < 2; i++) {
+        if (bounce[i]) cudaFreeHost(bounce[i]);
+        if (done[i]) cudaEventDestroy(done[i]);
+    }
+    if (stream) cudaStreamDestroy(stream);
+    close(fd);
+    cudaGetLastError();
+    return ok;
+}
+
+static h3_gpu_tensor *load_file(h3_gpu *gpu, const char *path, uint64_t offset, size_t elements,
+                                h3_gpu_dtype dtype) {
+    h3_gpu_tensor *tensor = tensor_new(gpu, nullptr, elements, dtype);
+    if (!tensor) return nullptr;
+    /* the block may have been recycled from a tensor whose last kernels are still queued */
+    cudaStreamSynchronize(gpu->stream);
+    char message[400];
+    if (!fill_from_file(tensor, path, offset, elements, dtype, message, sizeof(message))) {
+        h3b_fail(gpu, "%s", message);
+        h3_gpu_tensor_free(tensor);
+        return nullptr;
+    }
+    return tensor;
+}
+
+extern "C" h3_gpu_tensor *h3_gpu_tensor_load_bf16(h3_gpu *gpu, const char *path, uint64_t offset,
+                                                  size_t elements) {
+    return load_file(gpu, path, offset, elements, H3_GPU_BF16);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_load_f32(h3_gpu *gpu, const char *path, uint64_t offset,
+                                                 size_t elements) {
+    return load_file(gpu, path, offset, elements, H3_GPU_F32);
+}
+extern "C" int h3_gpu_tensor_read_file_bf16(h3_gpu_tensor *tensor, const char *path,
+                                            uint64_t offset, size_t elements, char *error,
+                                            size_t error_size) {
+    return fill_from_file(tensor, path, offset, elements, H3_GPU_BF16, error, error_size);
+}
+extern "C" int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *tensor, const char *path,
+                                              uint64_t offset, size_t elements, char *error,
+                                              size_t error_size) {
+    return fill_from_file(tensor, path, offset, elements, H3_GPU_BF16, error, error_size);
+}
+
+/* ----------------------------------------------------- casts and copies */
+
+__global__ void h3b_cast_f32_bf16(const float *in, uint16_t *out, size_t count) {
+    size_t i = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    bool aligned = ((reinterpret_cast<uintptr_t>(in) & 15u) | (reinterpret_cast<uintptr_t>(out) & 7u)) == 0;
+    if (aligned && i + 3 < count) {
+        float4 v = *reinterpret_cast<const float4 *>(in + i);
+        uint2 packed = {h3b_narrow2(v.x, v.y), h3b_narrow2(v.z, v.w)};
+        *reinterpret_cast<uint2 *>(out + i) = packed;
+    } else {
+        for (size_t e = i + 4 < count ? i + 4 : count; i < e; i++) out[i] = h3b_narrow(in[i]);
+    }
+}
+
+__global__ void h3b_cast_bf16_f32(const uint16_t *in, float *out, size_t count) {
+    size_t i = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    bool aligned = ((reinterpret_cast<uintptr_t>(in) & 7u) | (reinterpret_cast<uintptr_t>(out) & 15u)) == 0;
+    if (aligned && i + 3 < count) {
+        uint2 packed = *reinterpret_cast<const uint2 *>(in + i);
+        *reinterpret_cast<float4 *>(out + i) =
+            make_float4(h3b_lo(packed.x), h3b_hi(packed.x), h3b_lo(packed.y), h3b_hi(packed.y));
+    } else {
+        for (size_t e = i + 4 < count ? i + 4 : count; i < e; i++) out[i] = h3b_widen(in[i]);
+    }
+}
+
+extern "C" int h3_gpu_cast_f32_to_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                       const h3_gpu_tensor *input, uint32_t elements) {
+    if (!h3b_need(gpu, input, H3_GPU_F32, elements, "cast input") ||
+        !h3b_need(gpu, output, H3_GPU_BF16, elements, "cast output") || !h3b_need_command(gpu))
+        return 0;
+    if (elements) {
+        unsigned blocks = unsigned((size_t(elements) + 1023) / 1024);
+        h3b_cast_f32_bf16<<<blocks, 256, 0, gpu->stream>>>(h3b_ptr<float>(input),
+                                                          h3b_ptr<uint16_t>(output), elements);
+    }
+    return h3b_launched(gpu, "cast_f32_to_bf16");
+}
+
+extern "C" int h3_gpu_cast_bf16_to_f32(h3_gpu *gpu, h3_gpu_tensor *output,
+                                       const h3_gpu_tensor *input, uint32_t elements) {
+    if (!h3b_need(gpu, input, H3_GPU_BF16, elements, "cast input") ||
+        !h3b_need(gpu, output, H3_GPU_F32, elements, "cast output") || !h3b_need_command(gpu))
+        return 0;
+    if (elements) {
+        unsigned blocks = unsigned((size_t(elements) + 1023) / 1024);
+        h3b_cast_bf16_f32<<<blocks, 256, 0, gpu->stream>>>(h3b_ptr<uint16_t>(input),
+                                                          h3b_ptr<float>(output), elements);
+    }
+    return h3b_launched(gpu, "cast_bf16_to_f32");
+}
+
+static int device_copy(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offset,
+                       const h3_gpu_tensor *src, size_t src_offset, size_t elements,
+                       h3_gpu_dtype dtype) {
+    if (!dst || !src || dst->dtype != dtype || src->dtype != dtype)
+        return h3b_fail(gpu, "copy tensor has the wrong dtype");
+    if (dst_offset > dst->elements || elements > dst->elements - dst_offset ||
+        src_offset > src->elements || elements > src->elements - src_offset)
+        return h3b_fail(gpu, "copy range is out of bounds");
+    if (!h3b_need_command(gpu)) return 0;
+    size_t item = h3b_item_size(dtype);
+    if (elements) {
+        cudaError_t status = cudaMemcpyAsync(
+            static_cast<unsigned char *>(dst->data) + dst_offset * item,
+            static_cast<const unsigned char *>(src->data) + src_offset * item, elements * item,
+            cudaMemcpyDeviceToDevice, gpu->stream);
+        if (status != cudaSuccess) return h3b_fail_cuda(gpu, "device copy", status);
+    }
+    gpu->stats.blit_copies++;
+    return 1;
+}
+
+extern "C" int h3_gpu_copy_bf16(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offset,
+                                const h3_gpu_tensor *src, size_t src_offset, size_t elements) {
+    return device_copy(gpu, dst, dst_offset, src, src_offset, elements, H3_GPU_BF16);
+}
+extern "C" int h3_gpu_copy_f32(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offset,
+                               const h3_gpu_tensor *src, size_t src_offset, size_t elements) {
+    return device_copy(gpu, dst, dst_offset, src, src_offset, elements, H3_GPU_F32);
+}
+
+extern "C" int h3b200_probe(h3b200_device_info *info, char *error, size_t error_size) {
+    if (!info) return 0;
+    memset(info, 0, sizeof(*info));
+    cudaDeviceProp prop;
+    cudaError_t status = cudaGetDeviceProperties(&prop, g_device);
+    if (status != cudaSuccess) {
+        if (error && error_size)
+            snprintf(error, error_size, "no CUDA device: %s", cudaGetErrorString(status));
+        cudaGetLastError();
+        return 0;
+    }
+    snprintf(info->name, sizeof(info->name), "%s", prop.name);
+    info->total_memory = prop.totalGlobalMem;
+    info->compute_major = prop.major;
+    info->compute_minor = prop.minor;
+    info->multiprocessors = prop.multiProcessorCount;
+    return 1;
+}

@@ -1,0 +1,578 @@
+/* Dense projections of the DiT block: C[rows,n] = X[rows,k] . W[n,k]^T (+bias),
+ * BF16 operands, F32 accumulation, BF16 result. Replaces the reference's
+ * cuBLASLt wrapper (h3_cuda_gemm.cu) and the projection entry points of
+ * h3_cuda_core.cu behind the same C ABI.
+ *
+ * Tensor-core kernel (sm_100a): one persistent CTA per SM walks 128 x 256
+ * output tiles. Warp 0 feeds a 4-stage shared-memory ring with TMA
+ * (128-byte swizzle, 64-element K slabs, out-of-range rows and columns are
+ * zero-filled by the copy engine). One thread of warp 1 issues
+ * tcgen05.mma (M128 N256 K16, cta_group::1) with the F32 accumulator in
+ * tensor memory; the accumulator is double-buffered (2 x 256 columns) so that
+ * warps 2-5 drain tile i (tcgen05.ld, BF16 rounding, 16-byte stores) while the
+ * tensor core already works on tile i+1. Tiles are walked in groups of 16
+ * row-blocks so the CTAs that run together share operand slabs in L2.
+ *
+ * Epilogue variants: plain store (+bias), and SwiGLU for the MLP up
+ * projection, where a tile holds 128 gate columns and the matching 128 up
+ * columns so the [rows, 2*hidden] intermediate never goes to memory. The
+ * rounding points are the reference's: the fc1 result is rounded to BF16,
+ * then silu(gate)*up is rounded to BF16 (h3_cuda_core.cu:1067-1110).
+ *
+ * Every wait on an mbarrier is bounded: a thread that sees no progress for
+ * about a second records H3B_STATUS_GEMM_TIMEOUT, tells the rest of the CTA
+ * to stop, and the kernel returns normally (h3_gpu_submit reports it).
+ *
+ * A SIMT kernel (64 x 64 tiles, one sequential fmaf chain per output starting
+ * from the bias, so bit-identical to the reference's scalar kernel) serves
+ * shapes the TMA path cannot take (k or n not a multiple of 8, unaligned
+ * pointers, F32 operands) and problems too small to fill the machine.
+ */
+#include "h3b_common.cuh"
+#include "h3b_sm100.cuh"
+
+#include <cstdlib>
+
+namespace {
+
+/* ------------------------------------------------------ tensor-core GEMM */
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;                 /* one 128-byte swizzle row of BF16 */
+constexpr int STAGES = 4;
+constexpr int GROUP_M = 16;
+constexpr int A_BYTES = BM * BK * 2;   /* 16 KiB */
+constexpr int B_BYTES = BN * BK * 2;   /* 32 KiB */
+constexpr int TC_THREADS = 192;
+constexpr size_t TC_SMEM = size_t(STAGES) * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+
+struct TcArgs {
+    uint16_t *out;
+    const uint16_t *bias;
+    int *status;
+    uint32_t rows;        /* M */
+    uint32_t out_cols;    /* stored columns (n, or hidden for SwiGLU) */
+    uint32_t k_blocks;
+    uint32_t tiles_m, tiles_n;
+    uint32_t up_offset;   /* SwiGLU: weight row of the first up column (= hidden) */
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            TcArgs args) {
+    extern __shared__ uint8_t raw_smem[];
+    __shared__ int stop_flag;
+    const uint32_t base = (smem_u32(raw_smem) + 1023u) & ~1023u;
+    const uint32_t a_smem = base;
+    const uint32_t b_smem = base + STAGES * A_BYTES;
+    const uint32_t bars = b_smem + STAGES * B_BYTES;
+    const uint32_t full_bar = bars;                   /* STAGES x 8 */
+    const uint32_t empty_bar = bars + 8 * STAGES;     /* STAGES x 8 */
+    const uint32_t acc_full = bars + 16 * STAGES;     /* 2 x 8      */
+    const uint32_t acc_empty = acc_full + 16;         /* 2 x 8      */
+    const uint32_t tmem_holder = acc_empty + 16;      /* 4 bytes    */
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int *stop = &stop_flag;
+
+    if (threadIdx.x == 0) {
+        stop_flag = 0;
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(acc_full + 8 * i, 1);
+            mbar_init(acc_empty + 8 * i, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
+
+    const uint32_t total_tiles = args.tiles_m * args.tiles_n;
+    const uint32_t group_tiles = GROUP_M * args.tiles_n;
+
+    auto tile_coords = [&](uint32_t tile, uint32_t &m_blk, uint32_t &n_blk) {
+        uint32_t group = tile / group_tiles, local = tile % group_tiles;
+        uint32_t first_m = group * GROUP_M;
+        uint32_t group_m = min(args.tiles_m - first_m, uint32_t(GROUP_M));
+        m_blk = first_m + local % group_m;
+        n_blk = local / group_m;
+    };
+
+    if (warp == 0) {
+        /* ---- TMA producer ---- */
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+                uint32_t m_blk, n_blk;
+                tile_coords(tile, m_blk, n_blk);
+                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop)) { alive = false; break; }
+                    uint32_t bar = full_bar + 8 * stage;
+                    mbar_expect_tx(bar, A_BYTES + B_BYTES);
+                    tma_load_2d(a_smem + stage * A_BYTES, &map_a, bar, int(kb * BK), int(m_blk * BM));
+                    if (EPI == H3B_EPI_SWIGLU) {
+                        /* 128 gate rows then the matching 128 up rows of the weight */
+                        tma_load_2d(b_smem + stage * B_BYTES, &map_b, bar, int(kb * BK),
+                                    int(n_blk * 128));
+                        tma_load_2d(b_smem + stage * B_BYTES + B_BYTES / 2, &map_b, bar,
+                                    int(kb * BK), int(args.up_offset + n_blk * 128));
+                    } else {
+                        tma_load_2d(b_smem + stage * B_BYTES, &map_b, bar, int(kb * BK),
+                                    int(n_blk * BN));
+                        tma_load_2d(b_smem + stage * B_BYTES + B_BYTES / 2, &map_b, bar,
+                                    int(kb * BK), int(n_blk * BN + 128));
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ---- MMA issuer ---- */
+        if (lane == 0) {
+            constexpr uint32_t idesc = instruction_desc(BM, BN);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+                if (!mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop)) break;
+                tc_fence_after();
+                uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                    if (!mbar_wait(full_bar + 8 * stage, phase, stop)) { alive = false; break; }
+                    tc_fence_after();
+                    uint64_t a_desc = operand_desc(a_smem + stage * A_BYTES);
+                    uint64_t b_desc = operand_desc(b_smem + stage * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        /* 16 BF16 along K = 32 bytes = 2 descriptor address units */
+                        umma_bf16(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), idesc,
+                                  (kb | uint32_t(k)) != 0);
+                    }
+                    umma_commit(empty_bar + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!alive) break;
+                umma_commit(acc_full + 8 * acc);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        /* ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ---- */
+        const uint32_t quarter = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            uint32_t m_blk, n_blk;
+            tile_coords(tile, m_blk, n_blk);
+            if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop)) break;
+            tc_fence_after();
+            const uint32_t row = m_blk * BM + quarter * 32 + lane;
+            const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
+            const bool row_ok = row < args.rows;
+            if (EPI == H3B_EPI_SWIGLU) {
+                uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * 128;
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(lane_addr + c * 32, g);
+                    tmem_ld32(lane_addr + 128 + c * 32, u);
+                    tmem_ld_wait();
+                    uint32_t col0 = n_blk * 128 + c * 32;
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        float g0 = round_bf16(__uint_as_float(g[2 * i]));
+                        float g1 = round_bf16(__uint_as_float(g[2 * i + 1]));
+                        float u0 = round_bf16(__uint_as_float(u[2 * i]));
+                        float u1 = round_bf16(__uint_as_float(u[2 * i + 1]));
+                        packed[i] = pack_bf16(g0 / (1.0f + expf(-g0)) * u0,
+                                               g1 / (1.0f + expf(-g1)) * u1);
+                    }
+                    if (row_ok) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            if (col0 + v * 8 < args.out_cols)
+                                *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = make_uint4(
+                                    packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
+                                    packed[4 * v + 3]);
+                    }
+                }
+            } else {
+                uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + c * 32, r);
+                    tmem_ld_wait();
+                    uint32_t col0 = n_blk * BN + c * 32;
+                    uint32_t packed[16];
+                    if (args.bias) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            uint4 b = make_uint4(0, 0, 0, 0);
+                            if (col0 + v * 8 < args.out_cols)
+                                b = __ldg(reinterpret_cast<const uint4 *>(args.bias + col0 + v * 8));
+                            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                packed[4 * v + i] = pack_bf16(
+                                    __uint_as_float(r[8 * v + 2 * i]) + h3b_lo(bw[i]),
+                                    __uint_as_float(r[8 * v + 2 * i + 1]) + h3b_hi(bw[i]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                            packed[i] = pack_bf16(__uint_as_float(r[2 * i]),
+                                                   __uint_as_float(r[2 * i + 1]));
+                    }
+                    if (row_ok) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            if (col0 + v * 8 < args.out_cols)
+                                *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = make_uint4(
+                                    packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
+                                    packed[4 * v + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (stop_flag) {
+        if (threadIdx.x == 0) atomicMax(args.status, int(H3B_STATUS_GEMM_TIMEOUT));
+        /* give copies that may still be in flight time to land before the CTA retires */
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_free(tmem_base, 512);
+    }
+}
+
+/* ------------------------------------------------------------- SIMT GEMM */
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<uint16_t>(uint16_t v) { return h3b_widen(v); }
+
+template <typename T>
+__device__ __forceinline__ void from_f32(T *p, float v);
+template <>
+__device__ __forceinline__ void from_f32<float>(float *p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void from_f32<uint16_t>(uint16_t *p, float v) { *p = h3b_narrow(v); }
+
+/* 64 x 64 tile, 16 x 16 threads, 4 x 4 outputs per thread. Each output is one
+ * fmaf chain over k in increasing order starting from the bias. Output row r is
+ * written at row_map[r] when row_map is given. */
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+h3b_gemm_simt(const TIn *x, const TIn *w, const TIn *bias, TOut *out, const uint32_t *row_map,
+              uint32_t rows, uint32_t k, uint32_t n) {
+    __shared__ float xs[16][65];
+    __shared__ float ws[16][65];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const uint32_t row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
+    float acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t col = col0 + tx + 16 * j;
+        float start = (bias && col < n) ? to_f32<TIn>(bias[col]) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[i][j] = start;
+    }
+    for (uint32_t k0 = 0; k0 < k; k0 += 16) {
+        for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+            int r = e >> 4, kk = e & 15;
+            uint32_t gr = row0 + r, gc = col0 + r, gk = k0 + kk;
+            xs[kk][r] = (gr < rows && gk < k) ? to_f32<TIn>(x[size_t(gr) * k + gk]) : 0.0f;
+            ws[kk][r] = (gc < n && gk < k) ? to_f32<TIn>(w[size_t(gc) * k + gk]) : 0.0f;
+        }
+        __syncthreads();
+        uint32_t limit = min(16u, k - k0);
+        for (uint32_t kk = 0; kk < limit; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = xs[kk][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = ws[kk][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t row = row0 + ty + 16 * i;
+        if (row >= rows) continue;
+        size_t dst_row = row_map ? row_map[row] : row;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t col = col0 + tx + 16 * j;
+            if (col < n) from_f32<TOut>(out + dst_row * n + col, acc[i][j]);
+        }
+    }
+}
+
+template <typename TIn, typename TOut>
+void launch_simt(h3_gpu *gpu, const TIn *x, const TIn *w, const TIn *bias, TOut *out,
+                 const uint32_t *row_map, uint32_t rows, uint32_t k, uint32_t n) {
+    dim3 grid((n + 63) / 64, (rows + 63) / 64);
+    h3b_gemm_simt<TIn, TOut><<<grid, 256, 0, gpu->stream>>>(x, w, bias, out, row_map, rows, k, n);
+}
+
+/* ----------------------------------------------------------- tensor maps */
+
+/* [rows, k] row-major BF16 matrix, box = 64 columns x box_rows rows, 128-byte swizzle */
+bool make_map(CUtensorMap *map, const uint16_t *data, uint64_t rows, uint64_t k,
+              uint32_t box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return false;
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {k * 2};
+    cuuint32_t box[2] = {BK, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(data), dims,
+                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool env_flag(const char *name) {
+    const char *v = getenv(name);
+    return v && *v && strcmp(v, "0") != 0;
+}
+
+template <int EPI>
+int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
+              const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t weight_rows,
+              uint32_t out_cols, uint32_t tiles_n, uint32_t up_offset) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(h3b_gemm_tc<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(TC_SMEM)) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        configured = true;
+    }
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, x, rows, k, BM) || !make_map(&map_b, w, weight_rows, k, 128)) return 0;
+    TcArgs args;
+    args.out = out;
+    args.bias = bias;
+    args.status = gpu->status_device;
+    args.rows = rows;
+    args.out_cols = out_cols;
+    args.k_blocks = (k + BK - 1) / BK;
+    args.tiles_m = (rows + BM - 1) / BM;
+    args.tiles_n = tiles_n;
+    args.up_offset = up_offset;
+    uint32_t tiles = args.tiles_m * args.tiles_n;
+    uint32_t grid = tiles < uint32_t(gpu->sm_count) ? tiles : uint32_t(gpu->sm_count);
+    h3b_gemm_tc<EPI><<<grid, TC_THREADS, TC_SMEM, gpu->stream>>>(map_a, map_b, args);
+    return 1;
+}
+
+}  // namespace
+
+bool h3b_tensor_map_available() { return encode_tiled() != nullptr; }
+
+int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
+                  const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t n,
+                  h3b_gemm_epilogue epilogue, const char *what) {
+    /* n is the number of stored columns: for SwiGLU the weight has 2*n rows */
+    if (!rows || !n) return h3b_launched(gpu, what, H3B_LINEAR);
+    bool aligned = h3b_aligned16(out) && h3b_aligned16(x) && h3b_aligned16(w) &&
+                   (!bias || h3b_aligned16(bias));
+    bool tc_ok = aligned && k && k % 8 == 0 && n % 8 == 0 && !env_flag("H3B_NO_TENSOR_CORES") &&
+                 (epilogue == H3B_EPI_STORE || n % 128 == 0);
+    /* tiny problems are latency bound either way; keep them on the exact kernel */
+    if (double(rows) * n * k < 32.0 * 256 * 256) tc_ok = false;
+    if (tc_ok) {
+        int ok = epilogue == H3B_EPI_SWIGLU
+                     ? launch_tc<H3B_EPI_SWIGLU>(gpu, out, x, w, nullptr, rows, k, 2 * n, n,
+                                                 n / 128, n)
+                     : launch_tc<H3B_EPI_STORE>(gpu, out, x, w, bias, rows, k, n, n,
+                                                (n + BN - 1) / BN, 0);
+        if (ok) return h3b_launched(gpu, what, H3B_LINEAR);
+        return h3b_fail(gpu, "%s: cannot set up the tensor-core GEMM (tensor map or launch attribute)", what);
+    }
+    if (epilogue == H3B_EPI_SWIGLU) {
+        uint16_t *fused =
+            static_cast<uint16_t *>(h3b_workspace(gpu, size_t(rows) * n * 2 * sizeof(uint16_t)));
+        if (!fused) return h3b_fail(gpu, "%s: cannot allocate the MLP scratch", what);
+        launch_simt<uint16_t, uint16_t>(gpu, x, w, nullptr, fused, nullptr, rows, k, 2 * n);
+        if (!h3b_launched(gpu, what, H3B_LINEAR)) return 0;
+        return h3b_swiglu_launch(gpu, out, fused, rows, n);
+    }
+    launch_simt<uint16_t, uint16_t>(gpu, x, w, bias, out, nullptr, rows, k, n);
+    return h3b_launched(gpu, what, H3B_LINEAR);
+}
+
+/* ================================================================= C ABI */
+
+/* Which counter a projection bumps follows the reference's shape rule
+ * (h3_cuda_core.cu:838-841), so the statistics its tests assert are identical. */
+static h3b_kind linear_kind(uint32_t rows, uint32_t in_dim, uint32_t out_dim) {
+    return rows >= 32 && in_dim >= 256 && out_dim >= 256 ? H3B_LINEAR : H3B_DIRECT;
+}
+
+extern "C" int h3_gpu_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                                  const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                                  uint32_t rows, uint32_t input_dim, uint32_t output_dim) {
+    if (!h3b_need(gpu, input, H3_GPU_BF16, size_t(rows) * input_dim, "linear input") ||
+        !h3b_need(gpu, weight, H3_GPU_BF16, size_t(output_dim) * input_dim, "linear weight") ||
+        !h3b_need(gpu, output, H3_GPU_BF16, size_t(rows) * output_dim, "linear output") ||
+        (bias && !h3b_need(gpu, bias, H3_GPU_BF16, output_dim, "linear bias")) ||
+        !h3b_need_command(gpu))
+        return 0;
+    uint64_t before = gpu->stats.mps_linear_dispatches;
+    if (!h3b_gemm_bf16(gpu, h3b_ptr<uint16_t>(output), h3b_ptr<uint16_t>(input),
+                       h3b_ptr<uint16_t>(weight), bias ? h3b_ptr<uint16_t>(bias) : nullptr, rows,
+                       input_dim, output_dim, H3B_EPI_STORE, "linear_bf16"))
+        return 0;
+    if (linear_kind(rows, input_dim, output_dim) == H3B_DIRECT) {
+        gpu->stats.mps_linear_dispatches = before;
+        gpu->stats.direct_dispatches++;
+    }
+    return 1;
+}
+
+extern "C" int h3_gpu_linear_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                                 const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                                 uint32_t rows, uint32_t input_dim, uint32_t output_dim) {
+    if (!h3b_need(gpu, input, H3_GPU_F32, size_t(rows) * input_dim, "linear input") ||
+        !h3b_need(gpu, weight, H3_GPU_F32, size_t(output_dim) * input_dim, "linear weight") ||
+        !h3b_need(gpu, output, H3_GPU_F32, size_t(rows) * output_dim, "linear output") ||
+        (bias && !h3b_need(gpu, bias, H3_GPU_F32, output_dim, "linear bias")) ||
+        !h3b_need_command(gpu))
+        return 0;
+    if (rows && output_dim)
+        launch_simt<float, float>(gpu, h3b_ptr<float>(input), h3b_ptr<float>(weight),
+                                  bias ? h3b_ptr<float>(bias) : nullptr, h3b_ptr<float>(output),
+                                  nullptr, rows, input_dim, output_dim);
+    return h3b_launched(gpu, "linear_f32", linear_kind(rows, input_dim, output_dim));
+}
+
+extern "C" int h3_gpu_mlp_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                               const h3_gpu_tensor *fc1_weight, const h3_gpu_tensor *fc2_weight,
+                               uint32_t rows, uint32_t input_dim, uint32_t hidden_dim,
+                               uint32_t output_dim) {
+    if (!h3b_need(gpu, input, H3_GPU_BF16, size_t(rows) * input_dim, "MLP input") ||
+        !h3b_need(gpu, fc1_weight, H3_GPU_BF16, size_t(hidden_dim) * 2 * input_dim, "MLP fc1") ||
+        !h3b_need(gpu, fc2_weight, H3_GPU_BF16, size_t(output_dim) * hidden_dim, "MLP fc2") ||
+        !h3b_need(gpu, output, H3_GPU_BF16, size_t(rows) * output_dim, "MLP output") ||
+        !h3b_need_command(gpu))
+        return 0;
+    uint64_t linear_before = gpu->stats.mps_linear_dispatches;
+    uint64_t direct_before = gpu->stats.direct_dispatches;
+    if (rows && hidden_dim && output_dim) {
+        size_t act_bytes = (size_t(rows) * hidden_dim * sizeof(uint16_t) + 255) & ~size_t(255);
+        size_t fused_bytes = size_t(rows) * hidden_dim * 2 * sizeof(uint16_t);
+        /* activated | (unfused route only) fc1 output */
+        uint8_t *scratch = static_cast<uint8_t *>(h3b_workspace(gpu, act_bytes + fused_bytes));
+        if (!scratch) return h3b_fail(gpu, "cannot allocate the MLP scratch");
+        uint16_t *activated = reinterpret_cast<uint16_t *>(scratch);
+        if (env_flag("H3B_UNFUSED_MLP")) {
+            uint16_t *fused = reinterpret_cast<uint16_t *>(scratch + act_bytes);
+            if (!h3b_gemm_bf16(gpu, fused, h3b_ptr<uint16_t>(input), h3b_ptr<uint16_t>(fc1_weight),
+                               nullptr, rows, input_dim, hidden_dim * 2, H3B_EPI_STORE, "mlp fc1") ||
+                !h3b_swiglu_launch(gpu, activated, fused, rows, hidden_dim))
+                return 0;
+        } else if (!h3b_gemm_bf16(gpu, activated, h3b_ptr<uint16_t>(input),
+                                  h3b_ptr<uint16_t>(fc1_weight), nullptr, rows, input_dim,
+                                  hidden_dim, H3B_EPI_SWIGLU, "mlp fc1+swiglu")) {
+            return 0;
+        }
+        if (!h3b_gemm_bf16(gpu, h3b_ptr<uint16_t>(output), activated,
+                           h3b_ptr<uint16_t>(fc2_weight), nullptr, rows, hidden_dim, output_dim,
+                           H3B_EPI_STORE, "mlp fc2"))
+            return 0;
+    }
+    /* the reference counts an MLP as two projections whatever route ran */
+    gpu->stats.mps_linear_dispatches = linear_before + 2;
+    gpu->stats.direct_dispatches = direct_before;
+    return 1;
+}
+
+static int patch_common(h3_gpu *gpu, h3_gpu_tensor *output, size_t output_offset,
+                        size_t output_span, const h3_gpu_tensor *input, size_t input_offset,
+                        const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                        const h3_gpu_tensor *row_map, uint32_t rows, uint32_t input_dim,
+                        uint32_t output_dim, const char *what) {
+    /* the reference accepts exactly the model's patch shapes (h3_cuda_core.cu:929-931) */
+    if (output_dim != 5376 || (input_dim != 32 && input_dim != 96))
+        return h3b_fail(gpu, "unsupported fused patch projection shape");
+    size_t in_count = size_t(rows) * input_dim;
+    if (input_offset > SIZE_MAX - in_count || output_offset > SIZE_MAX - output_span)
+        return h3b_fail(gpu, "fused patch projection offset is out of range");
+    if (!h3b_need(gpu, input, H3_GPU_F32, input_offset + in_count, "patch projection input") ||
+        !h3b_need(gpu, weight, H3_GPU_F32, size_t(output_dim) * input_dim,
+                  "patch projection weight") ||
+        !h3b_need(gpu, output, H3_GPU_BF16, output_offset + output_span,
+                  "patch projection output") ||
+        (row_map && !h3b_need(gpu, row_map, H3_GPU_U32, rows, "patch projection row map")) ||
+        (bias && !h3b_need(gpu, bias, H3_GPU_F32, output_dim, "patch projection bias")) ||
+        !h3b_need_command(gpu))
+        return 0;
+    if (rows)
+        launch_simt<float, uint16_t>(gpu, h3b_ptr<float>(input, input_offset),
+                                     h3b_ptr<float>(weight), bias ? h3b_ptr<float>(bias) : nullptr,
+                                     h3b_ptr<uint16_t>(output, output_offset),
+                                     row_map ? h3b_ptr<uint32_t>(row_map) : nullptr, rows,
+                                     input_dim, output_dim);
+    return h3b_launched(gpu, what);
+}
+
+extern "C" int h3_gpu_patch_linear_bf16_offset(h3_gpu *gpu, h3_gpu_tensor *output,
+                                               size_t output_offset, const h3_gpu_tensor *input,
+                                               size_t input_offset, const h3_gpu_tensor *weight,
+                                               const h3_gpu_tensor *bias, uint32_t rows,
+                                               uint32_t input_dim, uint32_t output_dim) {
+    return patch_common(gpu, output, output_offset, size_t(rows) * output_dim, input, input_offset,
+                        weight, bias, nullptr, rows, input_dim, output_dim, "patch_linear_bf16");
+}
+
+extern "C" int h3_gpu_patch_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                        const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
+                                        const h3_gpu_tensor *bias, uint32_t rows,
+                                        uint32_t input_dim, uint32_t output_dim) {
+    return h3_gpu_patch_linear_bf16_offset(gpu, output, 0, input, 0, weight, bias, rows, input_dim,
+                                           output_dim);
+}
+
+extern "C" int h3_gpu_patch_linear_bf16_map(h3_gpu *gpu, h3_gpu_tensor *output,
+                                            const h3_gpu_tensor *input,
+                                            const h3_gpu_tensor *weight,
+                                            const h3_gpu_tensor *bias,
+                                            const h3_gpu_tensor *row_map, uint32_t output_rows,
+                                            uint32_t rows, uint32_t input_dim,
+                                            uint32_t output_dim) {
+    if (!row_map) return h3b_fail(gpu, "patch projection row map tensor has the wrong dtype");
+    return patch_common(gpu, output, 0, size_t(output_rows) * output_dim, input, 0, weight, bias,
+                        row_map, rows, input_dim, output_dim, "patch_linear_bf16_map");
+}

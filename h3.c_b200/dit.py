@@ -1,0 +1,244 @@
+"""Host-side driver of the DiT denoiser forward over the C ABI.
+
+Mirrors the reference's model layer for this path: the per-block op sequence of
+`run_block` (h3_dit.c:2008-2180) with the cross-block gate+adaLN carry, the activation
+aliasing of `allocate_activations` (h3_dit.c:1548-1551: attention_heads = mod_mlp = qkv,
+MLP output reuses attention_output), the step structure of `encode_forward`
+(h3_dit.c:2182-2528: patch projection, text rows copied in, 50 blocks, final heads) and
+the Euler update of `denoise_euler_gpu` (h3_dit.c:2805-2893). Every arithmetic step is a
+call into libh3b200.so with the reference's op names and argument meaning.
+
+Sequence parallelism (no counterpart in the reference): each rank owns a contiguous
+slice of rows; around attention the Q/K/V slices are regrouped by head and exchanged
+all-to-all so that each rank attends over the full sequence for heads/world heads
+(Ulysses), then exchanged back. The exchange itself is supplied by the caller (an object
+with all_to_all(out, inp)), e.g. torch.distributed over NCCL; this module only issues
+the layout kernels and attention.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+from .binding import BF16, F32, U32, Gpu, Tensor
+
+
+@dataclass
+class DitShape:
+    """Model constants (h3_dit.c:16-31, h3_dit_schedule.h:11-15)."""
+    hidden: int = 5376
+    heads: int = 56
+    head_dim: int = 128
+    ffn: int = 14336
+    blocks: int = 50
+    rope_half: int = 48
+    slots: int = 6
+    final_slots: int = 2
+    modalities: int = 3
+    time_dim: int = 2688
+    video_patch: int = 96
+    audio_channels: int = 32
+    eps: float = 1e-5
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def scale(self) -> float:
+        return 1.0 / math.sqrt(self.head_dim)
+
+    def gemm_flops_per_row(self) -> int:
+        h, i, f = self.hidden, self.inner, self.ffn
+        return 2 * (h * 3 * i + i * h + h * 2 * f + f * h)
+
+    def block_flops(self, rows: int) -> int:
+        return rows * self.gemm_flops_per_row() + 4 * rows * rows * self.heads * self.head_dim
+
+
+BLOCK_TENSORS = ("norm1", "norm2", "qkv", "q_norm", "k_norm", "out", "fc1", "fc2", "modulation")
+
+
+class BlockWeights:
+    """The eight checkpoint tensors of a block (h3_dit.c:518-525) + its modulation table."""
+
+    def __init__(self, **tensors: Tensor):
+        for name in BLOCK_TENSORS:
+            setattr(self, name, tensors[name])
+
+
+def block_tensor_shapes(s: DitShape, mod_rows: int) -> dict[str, int]:
+    return {
+        "norm1": s.hidden, "norm2": s.hidden,
+        "qkv": 3 * s.inner * s.hidden,
+        "q_norm": s.head_dim, "k_norm": s.head_dim,
+        "out": s.hidden * s.inner,
+        "fc1": 2 * s.ffn * s.hidden,
+        "fc2": s.hidden * s.ffn,
+        "modulation": mod_rows * s.slots * s.hidden,
+    }
+
+
+class SingleRank:
+    """Exchange for world size 1: attention sees the local rows directly."""
+    world, rank = 1, 0
+
+
+class Dit:
+    """Activations + op sequence for `rows_local` rows of a (possibly sharded) sequence."""
+
+    def __init__(self, gpu: Gpu, shape: DitShape, sequence: int, exchange=None,
+                 alloc=None):
+        self.gpu, self.s, self.sequence = gpu, shape, sequence
+        self.exchange = exchange or SingleRank()
+        world = self.exchange.world
+        if shape.heads % world:
+            raise ValueError("heads must divide by the number of ranks")
+        self.rows_local = (sequence + world - 1) // world
+        self.row_begin = min(sequence, self.exchange.rank * self.rows_local)
+        self.rows_valid = max(0, min(sequence, self.row_begin + self.rows_local) - self.row_begin)
+        rows, s = self.rows_local, shape
+        new = alloc or (lambda n: gpu.new(n, BF16))
+        self.hidden = new(rows * s.hidden)
+        self.mod_attention = new(rows * s.hidden)
+        self.qkv = new(rows * 3 * s.inner)          # also attention_heads and mod_mlp
+        self.query = new(rows * s.inner)
+        self.key = new(rows * s.inner)
+        self.value = new(rows * s.inner)
+        self.attention_output = new(rows * s.hidden)  # also the MLP output
+        self.attention_heads = self.qkv
+        self.mod_mlp = self.qkv
+        if world > 1:
+            # exchange buffers: [world][rows_local][heads/world][head_dim] x (q, k, v) and o
+            n = world * rows * (s.heads // world) * s.head_dim
+            self.send = [new(n) for _ in range(3)]
+            self.recv = [new(n) for _ in range(3)]
+            self.o_gathered = new(n)
+            self.o_returned = new(n)
+
+    # ------------------------------------------------------------ attention
+    def _attention(self):
+        g, s, rows = self.gpu, self.s, self.rows_local
+        ex = self.exchange
+        if ex.world == 1:
+            g.op("sdpa_bf16", self.attention_heads, self.query, self.key, self.value,
+                 self.sequence, s.heads, s.head_dim, s.scale)
+            return
+        hpr = s.heads // ex.world
+        for src, dst in zip((self.query, self.key, self.value), self.send):
+            g.op("h3x_ulysses_pack_heads", dst, src, rows, s.heads, s.head_dim, ex.world)
+        for snd, rcv in zip(self.send, self.recv):
+            ex.all_to_all(rcv, snd)
+        # gathered rows are in global order (rank-major); padding rows, if any, are the tail
+        g.op("sdpa_bf16", self.o_gathered, self.recv[0], self.recv[1], self.recv[2],
+             self.sequence, hpr, s.head_dim, s.scale)
+        ex.all_to_all(self.o_returned, self.o_gathered)
+        g.op("h3x_ulysses_unpack_heads", self.attention_heads, self.o_returned, rows, s.heads,
+             s.head_dim, ex.world)
+
+    # ---------------------------------------------------------------- block
+    def run_block(self, w: BlockWeights, row_map: Tensor, rope_cos: Tensor, rope_sin: Tensor,
+                  adaln_ready: bool, next_w: BlockWeights | None) -> bool:
+        """One block; returns whether the next block's attention adaLN is already in
+        mod_attention (the cross-block fusion of h3_dit.c:2139-2177)."""
+        g, s, rows = self.gpu, self.s, self.rows_local
+        if not adaln_ready:
+            g.op("adaln_bf16", self.mod_attention, self.hidden, w.norm1, w.modulation, row_map,
+                 rows, s.hidden, s.slots, 0, 1, s.eps)
+        g.op("grouped_qkv_linear_rope_bf16", self.query, self.key, self.value, self.qkv,
+             self.mod_attention, w.qkv, w.q_norm, w.k_norm, rope_cos, rope_sin, rows, s.hidden,
+             s.heads, s.head_dim, s.rope_half, s.eps)
+        self._attention()
+        g.op("linear_bf16", self.attention_output, self.attention_heads, w.out, None, rows,
+             s.inner, s.hidden)
+        g.op("gate_adaln_bf16", self.hidden, self.mod_mlp, self.hidden, self.attention_output,
+             w.norm2, w.modulation, w.modulation, row_map, rows, s.hidden, s.slots, 2, 3, 4, s.eps)
+        g.op("mlp_bf16", self.attention_output, self.mod_mlp, w.fc1, w.fc2, rows, s.hidden, s.ffn,
+             s.hidden)
+        if next_w is not None:
+            g.op("gate_adaln_bf16", self.hidden, self.mod_attention, self.hidden,
+                 self.attention_output, next_w.norm1, w.modulation, next_w.modulation, row_map,
+                 rows, s.hidden, s.slots, 5, 0, 1, s.eps)
+            return True
+        g.op("gate_bf16", self.hidden, self.hidden, self.attention_output, w.modulation, row_map,
+             rows, s.hidden, s.slots, 5)
+        return False
+
+    def run_blocks(self, blocks: list[BlockWeights], row_map: Tensor, rope_cos: Tensor,
+                   rope_sin: Tensor) -> None:
+        ready = False
+        for i, w in enumerate(blocks):
+            nxt = blocks[i + 1] if i + 1 < len(blocks) else None
+            ready = self.run_block(w, row_map, rope_cos, rope_sin, ready, nxt)
+            if i == int(len(blocks) * 0.6):
+                self.gpu.flush()     # the reference's mid-step command split (h3_dit.c:2403-2406)
+
+
+class DenoiseStep:
+    """encode_forward for a video(+text) layout: patch projection into `hidden`, text rows
+    copied in, the blocks, the final head, and (optionally) the Euler update."""
+
+    def __init__(self, dit: Dit, blocks: list[BlockWeights], *, video_rows: int, text_rows: int,
+                 patch_weight: Tensor, patch_bias: Tensor, text_hidden: Tensor,
+                 final_norm: Tensor, final_modulation: Tensor, final_weight: Tensor,
+                 final_bias: Tensor, row_map: Tensor, final_row_map: Tensor, rope_cos: Tensor,
+                 rope_sin: Tensor):
+        self.dit, self.blocks = dit, blocks
+        self.video_rows, self.text_rows = video_rows, text_rows
+        self.patch_weight, self.patch_bias, self.text_hidden = patch_weight, patch_bias, text_hidden
+        self.final_norm, self.final_modulation = final_norm, final_modulation
+        self.final_weight, self.final_bias = final_weight, final_bias
+        self.row_map, self.final_row_map = row_map, final_row_map
+        self.rope_cos, self.rope_sin = rope_cos, rope_sin
+        g, s = dit.gpu, dit.s
+        self.latent = g.new(max(1, video_rows) * s.video_patch, F32)       # patchified video rows
+        self.velocity = g.new(max(1, video_rows) * s.video_patch, BF16)
+        self.inverse = g.new(max(1, video_rows), F32)
+
+    def forward(self) -> None:
+        """Text rows first, then video rows (layout order of h3_layout_build: text segment
+        first, video target last). On a sharded run each rank projects its own video rows."""
+        d, g, s = self.dit, self.dit.gpu, self.dit.s
+        if self.text_rows:
+            g.op("copy_bf16", d.hidden, 0, self.text_hidden, 0, self.text_rows * s.hidden)
+        if self.video_rows:
+            g.op("patch_linear_bf16_offset", d.hidden, self.text_rows * s.hidden, self.latent, 0,
+                 self.patch_weight, self.patch_bias, self.video_rows, s.video_patch, s.hidden)
+        d.run_blocks(self.blocks, self.row_map, self.rope_cos, self.rope_sin)
+        if self.video_rows:
+            g.op("adaln_linear_bf16", self.velocity, self.inverse, d.hidden,
+                 self.text_rows * s.hidden, self.final_norm, self.final_modulation,
+                 self.final_row_map, self.final_weight, self.final_bias, self.video_rows, s.hidden,
+                 s.video_patch, s.final_slots, 0, 1, s.eps)
+
+    def euler(self, delta: float) -> None:
+        if self.video_rows:
+            self.dit.gpu.op("euler_bf16", self.latent, 0, self.velocity, self.velocity,
+                            self.video_rows * self.dit.s.video_patch, delta, 0.0)
+
+
+# ------------------------------------------------------------------ synthetic inputs
+
+def grid_positions(text_rows: int, t: int, h: int, w: int) -> np.ndarray:
+    """Positions (t, h, w) per row: text rows (index, 0, 0), then an integer t x h x w video grid."""
+    pos = np.zeros((text_rows + t * h * w, 3), np.float32)
+    pos[:text_rows, 0] = np.arange(text_rows)
+    tt, hh, ww = np.meshgrid(np.arange(t), np.arange(h), np.arange(w), indexing="ij")
+    pos[text_rows:, 0] = tt.reshape(-1)
+    pos[text_rows:, 1] = hh.reshape(-1)
+    pos[text_rows:, 2] = ww.reshape(-1)
+    return pos
+
+
+def default_inv_freq() -> np.ndarray:
+    """Stand-in for the checkpoint tensor rope.inv_freq[16] (h3_dit.c:887)."""
+    return (10000.0 ** (-np.arange(16, dtype=np.float64) / 16.0)).astype(np.float32)
+
+
+def row_map_for(text_rows: int, video_rows: int, time_row: int = 0) -> np.ndarray:
+    """row_map[row] = time_row * 3 + modality tag (video 0, text 1, audio 2;
+    h3_dit_schedule.c:448-482)."""
+    tags = np.concatenate([np.full(text_rows, 1, np.uint32), np.zeros(video_rows, np.uint32)])
+    return (time_row * 3 + tags).astype(np.uint32)

@@ -1,0 +1,311 @@
+/* h3b200 — B200 (sm_100a) device backend for the MiniMax-H3 DiT denoiser forward.
+ *
+ * This is the C ABI of libh3b200.so. The h3_gpu_* entry points have the names,
+ * argument order and return convention of the reference's device API
+ * (reference h3_gpu.h), so reference host code (h3_dit.c, h3_dit_schedule.c,
+ * h3_weights.c) compiled against the reference header links against this
+ * library unchanged. Each group below cites the reference declaration
+ * (h3_gpu.h:line) and the reference CUDA implementation it replaces.
+ *
+ * Conventions (reference h3_cuda_internal.h:126-185, h3_gpu_cuda.cu:871-911):
+ *   - every op returns 1 on success and 0 on failure; the message is read
+ *     with h3_gpu_error(); constructors return NULL on failure;
+ *   - ops fail unless issued between h3_gpu_begin() and h3_gpu_submit();
+ *   - work is enqueued in order on one stream; h3_gpu_submit() waits for it
+ *     and reports asynchronous failures;
+ *   - BF16 is raw uint16_t (exact widening, round-to-nearest-even narrowing),
+ *     sums are F32, weights are [out][in] row-major, activations row-major
+ *     with rows = tokens, offsets are in elements.
+ *
+ * Entry points of the reference API that are not on the DiT path (VAE
+ * convolutions, Qwen encoders, Metal-only int8/NAX routes) are exported too,
+ * as stubs that fail with a message, so that a full libh3 still links; this
+ * follows the reference's own practice (h3_cuda_dit.cu:1072-1216).
+ */
+#ifndef H3B200_H
+#define H3B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- types: h3_gpu.h:7-33 ------------------------------------------- */
+typedef struct h3_gpu h3_gpu;
+typedef struct h3_gpu_tensor h3_gpu_tensor;
+
+typedef enum { H3_GPU_F32 = 0, H3_GPU_BF16, H3_GPU_I8, H3_GPU_U32 } h3_gpu_dtype;
+
+typedef struct {
+    uint64_t allocated_bytes, live_bytes, peak_live_bytes, tensor_allocations;
+    uint64_t direct_dispatches;     /* hand kernels                        */
+    uint64_t mps_linear_dispatches; /* dense projections (tensor-core GEMM) */
+    uint64_t mps_conv_dispatches;
+    uint64_t mps_sdpa_dispatches;   /* attention calls                      */
+    uint64_t blit_copies, submissions;
+    double command_encode_seconds, command_wait_seconds, gpu_seconds;
+} h3_gpu_stats;
+
+/* ---- context: h3_gpu.h:35-51,100-110; h3_gpu_cuda.cu:80-170,871-933 --- */
+h3_gpu *h3_gpu_create(const char *unused_shader_path, char *error, size_t error_size);
+void h3_gpu_free(h3_gpu *gpu);
+int h3_gpu_is_m5(const h3_gpu *gpu);                /* 0 */
+int h3_gpu_has_nax_mlp(const h3_gpu *gpu);          /* 0 */
+int h3_gpu_has_int8_mlp(const h3_gpu *gpu);         /* 0 */
+int h3_gpu_prefers_gpu_sampler(const h3_gpu *gpu);  /* 1 */
+int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t ptr_count,
+                           const uint32_t *idx, size_t idx_count, uint32_t rows);
+int h3_gpu_begin(h3_gpu *gpu);
+int h3_gpu_continue(h3_gpu *gpu);
+int h3_gpu_submit(h3_gpu *gpu);
+const char *h3_gpu_error(const h3_gpu *gpu);
+int h3_gpu_get_stats(const h3_gpu *gpu, h3_gpu_stats *stats);
+void h3_gpu_profile_set_label(h3_gpu *gpu, const char *label);
+void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase);
+
+/* ---- tensors: h3_gpu.h:53-98; h3_gpu_cuda.cu:199-870 ----------------- */
+h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_i8(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *gpu, const float *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *gpu, const uint16_t *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *gpu, const uint32_t *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_load_bf16(h3_gpu *gpu, const char *path, uint64_t file_offset,
+                                       size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_load_f32(h3_gpu *gpu, const char *path, uint64_t file_offset,
+                                      size_t elements);
+int h3_gpu_tensor_read_file_bf16(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
+                                 size_t elements, char *error, size_t error_size);
+int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
+                                   size_t elements, char *error, size_t error_size);
+void h3_gpu_tensor_free(h3_gpu_tensor *tensor);
+size_t h3_gpu_tensor_elements(const h3_gpu_tensor *tensor);
+h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *tensor);
+int h3_gpu_tensor_read_f32(const h3_gpu_tensor *tensor, float *values, size_t elements);
+int h3_gpu_tensor_read_f32_range(const h3_gpu_tensor *tensor, size_t source_offset, float *values,
+                                 size_t elements);
+int h3_gpu_tensor_read_bf16(const h3_gpu_tensor *tensor, uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_f32(h3_gpu_tensor *tensor, const float *values, size_t elements);
+int h3_gpu_tensor_write_f32_range(h3_gpu_tensor *tensor, size_t destination_offset,
+                                  const float *values, size_t elements);
+int h3_gpu_tensor_write_bf16(h3_gpu_tensor *tensor, const uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *tensor, size_t destination_offset,
+                                   const uint16_t *values, size_t elements);
+
+/* ---- dense projections: h3_gpu.h:112-135,302-312; h3_cuda_core.cu:886-1140,
+ *      h3_cuda_gemm.cu:442-575. out = bf16(x . W^T + bias), F32 accumulate. -- */
+int h3_gpu_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                       const h3_gpu_tensor *weight, const h3_gpu_tensor *bias, uint32_t rows,
+                       uint32_t input_dim, uint32_t output_dim);
+int h3_gpu_linear_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                      const h3_gpu_tensor *weight, const h3_gpu_tensor *bias, uint32_t rows,
+                      uint32_t input_dim, uint32_t output_dim);
+/* fc1 -> SwiGLU (gate = first hidden_dim columns, up = last) -> fc2, each
+ * stage rounded to BF16. */
+int h3_gpu_mlp_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                    const h3_gpu_tensor *fc1_weight, const h3_gpu_tensor *fc2_weight,
+                    uint32_t rows, uint32_t input_dim, uint32_t hidden_dim, uint32_t output_dim);
+/* F32 rows x F32 weight (+bias) -> BF16 rows, optionally placed at a row
+ * offset or scattered through a row map (patch embedding into `hidden`). */
+int h3_gpu_patch_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                             const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                             uint32_t rows, uint32_t input_dim, uint32_t output_dim);
+int h3_gpu_patch_linear_bf16_offset(h3_gpu *gpu, h3_gpu_tensor *output, size_t output_offset,
+                                    const h3_gpu_tensor *input, size_t input_offset,
+                                    const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                                    uint32_t rows, uint32_t input_dim, uint32_t output_dim);
+int h3_gpu_patch_linear_bf16_map(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                                 const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                                 const h3_gpu_tensor *row_map, uint32_t output_rows,
+                                 uint32_t rows, uint32_t input_dim, uint32_t output_dim);
+
+/* ---- adaLN / gate / final head: h3_gpu.h:154-166,387-430;
+ *      h3_cuda_dit.cu:94-332,550-795 ------------------------------------ */
+int h3_gpu_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                      const h3_gpu_tensor *norm_weight, const h3_gpu_tensor *modulation,
+                      const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                      uint32_t slots, uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+int h3_gpu_adaln_bf16_offset(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                             size_t input_offset, const h3_gpu_tensor *norm_weight,
+                             const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map,
+                             uint32_t rows, uint32_t width, uint32_t slots, uint32_t shift_slot,
+                             uint32_t scale_slot, float epsilon);
+int h3_gpu_adaln_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                     const h3_gpu_tensor *norm_weight, const h3_gpu_tensor *modulation,
+                     const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width, uint32_t slots,
+                     uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                     const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
+                     const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width, uint32_t slots,
+                     uint32_t gate_slot);
+int h3_gpu_gate_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                    const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
+                    const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width, uint32_t slots,
+                    uint32_t gate_slot);
+/* gated_residual = bf16(residual + branch*gate); output = adaLN(gated_residual).
+ * gated_residual may alias residual. */
+int h3_gpu_gate_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *gated_residual, h3_gpu_tensor *output,
+                           const h3_gpu_tensor *residual, const h3_gpu_tensor *branch,
+                           const h3_gpu_tensor *norm_weight,
+                           const h3_gpu_tensor *gate_modulation,
+                           const h3_gpu_tensor *norm_modulation, const h3_gpu_tensor *row_map,
+                           uint32_t rows, uint32_t width, uint32_t slots, uint32_t gate_slot,
+                           uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+/* final head: adaLN rounded to BF16, then Linear(width -> output_dim)+bias;
+ * also stores the per-row inverse RMS (F32). */
+int h3_gpu_adaln_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *inverse,
+                             const h3_gpu_tensor *input, size_t input_offset,
+                             const h3_gpu_tensor *norm_weight, const h3_gpu_tensor *modulation,
+                             const h3_gpu_tensor *row_map, const h3_gpu_tensor *weight,
+                             const h3_gpu_tensor *bias, uint32_t rows, uint32_t width,
+                             uint32_t output_dim, uint32_t slots, uint32_t shift_slot,
+                             uint32_t scale_slot, float epsilon);
+
+/* ---- QKV split + per-head RMSNorm + RoPE, attention: h3_gpu.h:444-482,504-514;
+ *      h3_cuda_attention.cu:173-351,2622-2779,2933-3123 ------------------- */
+int h3_gpu_qkv_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                         h3_gpu_tensor *value, const h3_gpu_tensor *qkv,
+                         const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                         const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                         uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                         uint32_t rope_half, float epsilon);
+int h3_gpu_grouped_qkv_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                                 h3_gpu_tensor *value, const h3_gpu_tensor *qkv,
+                                 const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                                 const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                 uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                                 uint32_t rope_half, float epsilon);
+int h3_gpu_grouped_qkv_linear_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                                        h3_gpu_tensor *value, h3_gpu_tensor *qkv,
+                                        const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
+                                        const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                                        const h3_gpu_tensor *rope_cos,
+                                        const h3_gpu_tensor *rope_sin, uint32_t rows,
+                                        uint32_t input_dim, uint32_t heads, uint32_t head_dim,
+                                        uint32_t rope_half, float epsilon);
+/* non-causal softmax(q k^T * scale) v over all `sequence` rows, per head;
+ * q/k/v are [row][head][head_dim]; output likewise, or [head][row][head_dim]. */
+int h3_gpu_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                     const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t sequence,
+                     uint32_t heads, uint32_t head_dim, float scale);
+int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *output,
+                                       const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                       const h3_gpu_tensor *value, uint32_t sequence,
+                                       uint32_t heads, uint32_t head_dim, float scale);
+
+/* ---- elementwise / row ops: h3_gpu.h:136-149,365-370,515-517,551-556,616-622;
+ *      h3_cuda_core.cu:15-210, h3_gpu_cuda.cu:937-1030, h3_cuda_dit.cu:536-548 -- */
+int h3_gpu_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *fused,
+                       uint32_t rows, uint32_t width);
+int h3_gpu_silu_mul_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *gate,
+                         const h3_gpu_tensor *up, uint32_t elements);
+int h3_gpu_silu_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                    uint32_t elements);
+int h3_gpu_silu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                     uint32_t elements);
+int h3_gpu_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                         const h3_gpu_tensor *weight, uint32_t rows, uint32_t width,
+                         float epsilon);
+int h3_gpu_add_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *left,
+                    const h3_gpu_tensor *right, uint32_t elements);
+int h3_gpu_sub_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *left,
+                    const h3_gpu_tensor *right, uint32_t elements);
+int h3_gpu_cast_f32_to_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                            uint32_t elements);
+int h3_gpu_cast_bf16_to_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                            uint32_t elements);
+int h3_gpu_copy_bf16(h3_gpu *gpu, h3_gpu_tensor *destination, size_t destination_offset,
+                     const h3_gpu_tensor *source, size_t source_offset, size_t elements);
+int h3_gpu_copy_f32(h3_gpu *gpu, h3_gpu_tensor *destination, size_t destination_offset,
+                    const h3_gpu_tensor *source, size_t source_offset, size_t elements);
+/* sample += delta * (last + ratio * (last - previous)); F32 sample, BF16 velocities */
+int h3_gpu_euler_bf16(h3_gpu *gpu, h3_gpu_tensor *sample, size_t sample_offset,
+                      const h3_gpu_tensor *last, const h3_gpu_tensor *previous,
+                      uint32_t elements, float delta, float ratio);
+
+/* ---- token reduction: h3_gpu.h:557-613; h3_cuda_dit.cu:336-534,797-1049 -- */
+int h3_gpu_token_pool_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                           size_t input_offset, h3_gpu_tensor *original, size_t original_offset,
+                           h3_gpu_tensor *baseline, size_t baseline_offset,
+                           const h3_gpu_tensor *baseline_indices, const h3_gpu_tensor *pairs,
+                           uint32_t input_rows, uint32_t rows, uint32_t baseline_rows,
+                           uint32_t width);
+int h3_gpu_token_pool_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *residual, h3_gpu_tensor *output,
+                                 const h3_gpu_tensor *input, size_t input_offset,
+                                 h3_gpu_tensor *original, size_t original_offset,
+                                 h3_gpu_tensor *baseline, size_t baseline_offset,
+                                 const h3_gpu_tensor *baseline_indices,
+                                 const h3_gpu_tensor *pairs, const h3_gpu_tensor *norm_weight,
+                                 const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map,
+                                 uint32_t input_rows, uint32_t rows, uint32_t baseline_rows,
+                                 uint32_t width, uint32_t slots, uint32_t shift_slot,
+                                 uint32_t scale_slot, float epsilon);
+int h3_gpu_token_expand_delta_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                   const h3_gpu_tensor *original, size_t original_offset,
+                                   const h3_gpu_tensor *reduced, const h3_gpu_tensor *baseline,
+                                   size_t baseline_offset,
+                                   const h3_gpu_tensor *baseline_indices,
+                                   const h3_gpu_tensor *parents, uint32_t rows,
+                                   uint32_t reduced_rows, uint32_t baseline_rows, uint32_t width,
+                                   uint32_t exact_prefix_rows, float update_scale);
+int h3_gpu_token_expand_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *residual, h3_gpu_tensor *output,
+                                   const h3_gpu_tensor *original, size_t original_offset,
+                                   const h3_gpu_tensor *reduced, const h3_gpu_tensor *baseline,
+                                   size_t baseline_offset,
+                                   const h3_gpu_tensor *baseline_indices,
+                                   const h3_gpu_tensor *parents,
+                                   const h3_gpu_tensor *norm_weight,
+                                   const h3_gpu_tensor *modulation,
+                                   const h3_gpu_tensor *row_map, uint32_t rows,
+                                   uint32_t reduced_rows, uint32_t baseline_rows, uint32_t width,
+                                   uint32_t exact_prefix_rows, float update_scale, uint32_t slots,
+                                   uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+
+/* ---- device probe: h3_cuda.h:9; h3_gpu_cuda.cu:1032-1046 ----------------- */
+typedef struct {
+    char name[256];
+    uint64_t total_memory;
+    int compute_major, compute_minor, multiprocessors;
+} h3b200_device_info;
+int h3b200_probe(h3b200_device_info *info, char *error, size_t error_size);
+
+/* ====================================================================== *
+ * Extensions (no counterpart in the reference, which is single-device and
+ * single-stream). They let a host process that owns device memory and
+ * streams (one process per GPU) drive the same ops, and provide the
+ * sequence-parallel (Ulysses) layout changes around attention.
+ * ====================================================================== */
+
+/* Select the device for contexts created afterwards by this thread
+ * (the reference hard-wires device 0, h3_gpu_cuda.cu:98-99). */
+int h3x_set_device(int device);
+/* Enqueue all later work of this context on `cuda_stream` (a cudaStream_t;
+ * NULL = the legacy default stream, which is what the reference uses). */
+int h3x_set_stream(h3_gpu *gpu, void *cuda_stream);
+/* Non-owning tensor over caller-owned device memory (not freed with the tensor). */
+h3_gpu_tensor *h3x_tensor_wrap(h3_gpu *gpu, void *device_pointer, size_t elements,
+                               h3_gpu_dtype dtype);
+void *h3x_tensor_device_pointer(const h3_gpu_tensor *tensor);
+/* Last asynchronous kernel status word (0 = ok), read after h3_gpu_submit(). */
+int h3x_kernel_status(h3_gpu *gpu);
+
+/* Ulysses exchange layout. `packed` holds, for each of `world` peers p, the
+ * contiguous block [rows_local][heads/world][head_dim] of heads
+ * [p*heads/world, (p+1)*heads/world) taken from src = [rows_local][heads][head_dim].
+ * After an all-to-all of equal blocks, rank r holds [world][rows_local][heads/world][hd]
+ * = all rows of its head slice, row-sharded order preserved. */
+int h3x_ulysses_pack_heads(h3_gpu *gpu, h3_gpu_tensor *packed, const h3_gpu_tensor *src,
+                           uint32_t rows_local, uint32_t heads, uint32_t head_dim,
+                           uint32_t world);
+/* Inverse for the attention output: src = [world][rows_local][heads/world][hd]
+ * (after the return all-to-all) -> dst = [rows_local][heads][hd]. */
+int h3x_ulysses_unpack_heads(h3_gpu *gpu, h3_gpu_tensor *dst, const h3_gpu_tensor *src,
+                             uint32_t rows_local, uint32_t heads, uint32_t head_dim,
+                             uint32_t world);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* H3B200_H */

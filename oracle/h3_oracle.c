@@ -117,6 +117,7 @@ uint64_t h3o_named_seed(uint64_t seed, const char *name) {
  * kernel. Vectorised across a block of rows so every output keeps its own
  * sequential chain. */
 #define RB 32
+#define CB 64
 static void gemm_rows_seq(float *out, size_t out_stride, const float *x_f32,
                           const uint16_t *x_bf16, size_t x_stride,
                           const float *w_f32, const uint16_t *w_bf16,
@@ -124,24 +125,34 @@ static void gemm_rows_seq(float *out, size_t out_stride, const float *x_f32,
                           uint32_t out_dim) {
     if (!rows || !out_dim) return;
     uint32_t row_blocks = (rows + RB - 1) / RB;
+    uint32_t col_blocks = (out_dim + CB - 1) / CB;
+    long tasks = (long)row_blocks * col_blocks;
 #pragma omp parallel
     {
         float *xt = (float *)aligned_alloc(64, (size_t)(in_dim ? in_dim : 1) *
                                                    RB * sizeof(float));
-#pragma omp for schedule(dynamic, 1)
-        for (uint32_t rb = 0; rb < row_blocks; rb++) {
+        long cached_rb = -1;
+        /* consecutive tasks share a row block, so each thread transposes it rarely */
+#pragma omp for schedule(dynamic, 4)
+        for (long task = 0; task < tasks; task++) {
+            uint32_t rb = (uint32_t)(task / col_blocks);
+            uint32_t cb = (uint32_t)(task % col_blocks);
             uint32_t r0 = rb * RB;
             uint32_t live = rows - r0 < RB ? rows - r0 : RB;
-            for (uint32_t k = 0; k < in_dim; k++)
-                for (uint32_t i = 0; i < RB; i++) {
-                    float v = 0.0f;
-                    if (i < live) {
-                        size_t idx = (size_t)(r0 + i) * x_stride + k;
-                        v = x_f32 ? x_f32[idx] : widen(x_bf16[idx]);
+            if (cached_rb != (long)rb) {
+                for (uint32_t k = 0; k < in_dim; k++)
+                    for (uint32_t i = 0; i < RB; i++) {
+                        float v = 0.0f;
+                        if (i < live) {
+                            size_t idx = (size_t)(r0 + i) * x_stride + k;
+                            v = x_f32 ? x_f32[idx] : widen(x_bf16[idx]);
+                        }
+                        xt[(size_t)k * RB + i] = v;
                     }
-                    xt[(size_t)k * RB + i] = v;
-                }
-            for (uint32_t c = 0; c < out_dim; c++) {
+                cached_rb = rb;
+            }
+            uint32_t c_end = (cb + 1) * CB < out_dim ? (cb + 1) * CB : out_dim;
+            for (uint32_t c = cb * CB; c < c_end; c++) {
                 float acc[RB];
                 float start = bias ? bias[c] : 0.0f;
                 for (uint32_t i = 0; i < RB; i++) acc[i] = start;

@@ -1,0 +1,69 @@
+"""CPU-side checks of the drop-in boundary: the shared library loads without a GPU, exports
+every symbol include/h3b200.h declares plus every h3_gpu_* symbol of the reference's device
+API (so a full libh3 links), and fails loudly - not silently - when no device is present."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+LIB = ROOT / "h3.c_b200" / "libh3b200.so"
+REFERENCE_HEADER = Path("/root/reference/h3_gpu.h")
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import __graft_entry__ as entry
+    if not LIB.exists():
+        entry.build()
+    return entry.load_package()
+
+
+def exported_symbols():
+    out = subprocess.run(["nm", "-D", "--defined-only", str(LIB)], capture_output=True, text=True,
+                         check=True).stdout
+    return {line.split()[-1] for line in out.splitlines() if line.strip()}
+
+
+def test_header_symbols_are_exported(pkg):
+    declared = pkg.declared_functions()
+    assert len(declared) >= 70
+    missing = sorted(set(declared) - exported_symbols())
+    assert not missing, missing
+
+
+@pytest.mark.skipif(not REFERENCE_HEADER.exists(), reason="reference tree not present")
+def test_every_reference_entry_point_is_exported(pkg):
+    names = set(re.findall(r"\b(h3_gpu_[a-z0-9_]+)\s*\(", REFERENCE_HEADER.read_text()))
+    assert len(names) > 100
+    missing = sorted(names - exported_symbols())
+    assert not missing, missing
+
+
+def test_prototypes_parse_to_the_expected_ctypes(pkg):
+    d = pkg.declared_functions()
+    assert d["h3_gpu_create"] == (C.c_void_p, [C.c_char_p, C.c_char_p, C.c_size_t])
+    assert d["h3_gpu_linear_bf16"][1] == [C.c_void_p] * 5 + [C.c_uint32] * 3
+    assert d["h3_gpu_euler_bf16"][1] == [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                         C.c_uint32, C.c_float, C.c_float]
+    assert d["h3_gpu_sdpa_bf16"][1] == [C.c_void_p] * 5 + [C.c_uint32] * 3 + [C.c_float]
+
+
+def test_no_device_fails_loudly(pkg):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(pkg.H3Error):
+        pkg.Gpu(0)
+
+
+def test_product_does_not_reference_the_oracle():
+    """The shipped package must not import, link or call anything under oracle/."""
+    for path in (ROOT / "h3.c_b200").rglob("*"):
+        if path.suffix in {".py", ".cu", ".cuh", ".h"}:
+            text = path.read_text()
+            assert "h3_oracle" not in text and "oracle/" not in text, path
+    needed = subprocess.run(["ldd", str(LIB)], capture_output=True, text=True).stdout
+    assert "oracle" not in needed
