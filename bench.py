@@ -236,7 +236,7 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     gen.manual_seed(seed)
     dit = pkg.Dit(gpu, s, sequence, exchange=exchange, alloc=lambda n: mem.bf16(n))
     time_rows = 2
-    silu_time = mem.bf16(time_rows * s.time_dim, std=0.4, generator=gen)
+    silu_time = mem.bf16(time_rows * s.time_dim, std=0.125, generator=gen)   # modulation std ~0.13
     mod_cols = s.modalities * s.slots * s.hidden
     proj_w = mem.bf16(mod_cols * s.time_dim)
     proj_b = mem.bf16(mod_cols)
@@ -268,8 +268,8 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     r0, rows = dit.row_begin, dit.rows_local
     video_rows_total = sequence - text_rows
     sys.path.insert(0, str(ROOT / "oracle"))
-    t_len = max(1, video_rows_total // 1024)
-    pos = np.zeros((dit.rows_local * exchange.world, 3), np.float32)
+    world = dit.exchange.world
+    pos = np.zeros((dit.rows_local * world, 3), np.float32)
     pos[:text_rows, 0] = np.arange(text_rows)
     idx = np.arange(video_rows_total)
     pos[text_rows:sequence, 0] = idx // 1024 if video_rows_total >= 1024 else 0
@@ -283,7 +283,7 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     rope_cos, rope_sin = mem.bf16(rows * 48), mem.bf16(rows * 48)
     mem.torch_of(rope_cos).copy_(cos.reshape(-1).to(torch.bfloat16))
     mem.torch_of(rope_sin).copy_(sin.reshape(-1).to(torch.bfloat16))
-    tags = np.zeros(dit.rows_local * exchange.world, np.uint32)
+    tags = np.zeros(dit.rows_local * world, np.uint32)
     tags[:text_rows] = 1
     row_map = gpu.u32(tags[r0:r0 + rows] + 3 * 1)
     local_text = max(0, min(text_rows, r0 + dit.rows_valid) - r0)

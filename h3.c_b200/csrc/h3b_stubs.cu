@@ -18,14 +18,21 @@
                                    "libh3b200");                                         \
     }
 
-/* Metal 4 TensorOps / NAX int8 routes (capability probes answer 0) */
-H3B_NOT_ON_DIT_PATH(h3_gpu_quantize_weight_int8)
-H3B_NOT_ON_DIT_PATH(h3_gpu_linear_int8_bf16)
-H3B_NOT_ON_DIT_PATH(h3_gpu_linear_int8_head_major_bf16)
-H3B_NOT_ON_DIT_PATH(h3_gpu_mlp_int8_bf16)
-H3B_NOT_ON_DIT_PATH(h3_gpu_mlp_nax_bf16)
-H3B_NOT_ON_DIT_PATH(h3_gpu_gate_adaln_quantize_int8)
-H3B_NOT_ON_DIT_PATH(h3_gpu_grouped_qkv_linear_rope_int8)
+/* Metal 4 TensorOps / NAX int8 routes. The capability probes answer 0, so the model
+ * layer never takes them; the message keeps the wording the reference's own test looks
+ * for (tests/test_cuda_dit.c:771-817). */
+#define H3B_METAL_ONLY(name)                                                             \
+    extern "C" int name(h3_gpu *gpu) {                                                   \
+        return h3b_fail(gpu, #name " is a Metal-only route and is not available in the " \
+                                   "CUDA backend");                                      \
+    }
+H3B_METAL_ONLY(h3_gpu_quantize_weight_int8)
+H3B_METAL_ONLY(h3_gpu_linear_int8_bf16)
+H3B_METAL_ONLY(h3_gpu_linear_int8_head_major_bf16)
+H3B_METAL_ONLY(h3_gpu_mlp_int8_bf16)
+H3B_METAL_ONLY(h3_gpu_mlp_nax_bf16)
+H3B_METAL_ONLY(h3_gpu_gate_adaln_quantize_int8)
+H3B_METAL_ONLY(h3_gpu_grouped_qkv_linear_rope_int8)
 /* audio / video VAE */
 H3B_NOT_ON_DIT_PATH(h3_gpu_conv1d_f32)
 H3B_NOT_ON_DIT_PATH(h3_gpu_conv1d_stride_f32)

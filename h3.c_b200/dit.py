@@ -81,6 +81,24 @@ def block_tensor_shapes(s: DitShape, mod_rows: int) -> dict[str, int]:
     }
 
 
+def shard_rows(sequence: int, world: int, rank: int) -> tuple[int, int, int]:
+    """(rows_local, row_begin, rows_valid): every rank holds rows_local = ceil(S/world) rows;
+    the last ranks may hold fewer valid rows, padding sits at the global tail."""
+    rows_local = (sequence + world - 1) // world
+    begin = min(sequence, rank * rows_local)
+    valid = max(0, min(sequence, begin + rows_local) - begin)
+    return rows_local, begin, valid
+
+
+def ulysses_pack_order(rows_local: int, heads: int, world: int) -> np.ndarray:
+    """Index map of h3x_ulysses_pack_heads in units of one head vector:
+    packed[(p*rows_local + r)*hpr + hl] = src[r*heads + p*hpr + hl]. Host-side layout
+    bookkeeping only (tests and buffer sizing); the data movement is the CUDA kernel."""
+    hpr = heads // world
+    p, r, hl = np.meshgrid(np.arange(world), np.arange(rows_local), np.arange(hpr), indexing="ij")
+    return (r * heads + p * hpr + hl).reshape(-1)
+
+
 class SingleRank:
     """Exchange for world size 1: attention sees the local rows directly."""
     world, rank = 1, 0
@@ -96,9 +114,8 @@ class Dit:
         world = self.exchange.world
         if shape.heads % world:
             raise ValueError("heads must divide by the number of ranks")
-        self.rows_local = (sequence + world - 1) // world
-        self.row_begin = min(sequence, self.exchange.rank * self.rows_local)
-        self.rows_valid = max(0, min(sequence, self.row_begin + self.rows_local) - self.row_begin)
+        self.rows_local, self.row_begin, self.rows_valid = shard_rows(sequence, world,
+                                                                      self.exchange.rank)
         rows, s = self.rows_local, shape
         new = alloc or (lambda n: gpu.new(n, BF16))
         self.hidden = new(rows * s.hidden)

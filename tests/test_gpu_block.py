@@ -75,6 +75,51 @@ def test_block_matches_reference_cuda_backend(pkg):
     print(f"config-1 block (S=1664) vs reference CUDA backend: rel_l2={r:.3e} max_abs={m:.3e}")
 
 
+@pytest.mark.parametrize("heads", [24, 56])
+def test_standalone_attention_config2(pkg, heads):
+    """BASELINE config 2: [1, heads, 6400 tokens (6,144 video on a 6x32x32 grid + 256 text), 128],
+    N(0,1) seed 3, 3-D RoPE on video rows and 1-D on text rows applied by the QKV op first.
+    Checked against the oracle on a sample of query rows (full attention over all keys) and,
+    where it was built, against the reference's CUDA backend on every row."""
+    seq, hd, text = 6400, 128, 256
+    n = seq * heads * hd
+    rng = np.random.default_rng(3)
+    qkv = o.to_bf16(rng.standard_normal(3 * n, dtype=np.float32))
+    pos = np.zeros((seq, 3), np.float32)
+    pos[:text, 0] = np.arange(text)
+    idx = np.arange(seq - text)
+    pos[text:, 0], pos[text:, 1], pos[text:, 2] = idx // 1024, (idx % 1024) // 32, idx % 32
+    cos, sin = o.rope_tables(pos, (10000.0 ** (-np.arange(16) / 16.0)).astype(np.float32))
+    one = np.full(hd, o.to_bf16(np.ones(1, np.float32))[0], np.uint16)
+    scale = 1.0 / np.sqrt(hd)
+    outs = {}
+    for name, path in (("b200", None), ("reference", REF_CUDA)):
+        if path is not None and not path.exists():
+            continue
+        gpu = pkg.Gpu(0, lib_path=path)
+        try:
+            tq, tk, tv, to = (gpu.new(n, pkg.BF16) for _ in range(4))
+            t = [gpu.bf16(a) for a in (qkv, one, one, cos, sin)]
+            gpu.begin()
+            gpu.op("grouped_qkv_rope_bf16", tq, tk, tv, *t, seq, heads, hd, 48, 1e-5)
+            gpu.op("sdpa_bf16", to, tq, tk, tv, seq, heads, hd, scale)
+            gpu.submit()
+            outs[name] = (to.read(), tq.read(), tk.read(), tv.read())
+        finally:
+            gpu.close()
+    got, q, k, v = outs["b200"]
+    rows = (3000, 3064)
+    want = o.sdpa_bf16(q, k, v, seq, heads, hd, scale, 0, round_p=0, rows=rows)
+    sl = slice(rows[0] * heads * hd, rows[1] * heads * hd)
+    r, m = block_metrics(got[sl], want[sl])
+    print(f"config-2 attention heads={heads} vs CPU oracle (64 query rows): rel_l2={r:.3e} max_abs={m:.3e}")
+    assert r <= 4e-3 and m <= 2e-2
+    if "reference" in outs:
+        r, m = block_metrics(got, outs["reference"][0])
+        print(f"config-2 attention heads={heads} vs reference CUDA backend: rel_l2={r:.3e} max_abs={m:.3e}")
+        assert r <= 4e-3 and m <= 2e-2
+
+
 @pytest.mark.skipif(not REF_DIT_TESTS.exists(), reason="reference test program was not built")
 def test_reference_dit_op_tests_pass_on_this_backend():
     """tests/test_cuda_dit.c of the reference (12 fused DiT ops against its own CPU references,
