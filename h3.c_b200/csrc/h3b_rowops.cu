@@ -688,6 +688,98 @@ extern "C" int h3_gpu_adaln_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
                          H3B_EPI_STORE, "adaln_linear_bf16");
 }
 
+/* ------------------------------------------------- final head, no allocation */
+
+/* Scratch for h3x_adaln_linear_bf16_noalloc: the BF16-rounded adaLN rows that sit
+ * between the normalisation kernel and the projection. It is part of the library
+ * image, so every GPU that loads the library holds these 8 MiB until the process
+ * exits. */
+constexpr size_t kNoAllocScratchElements = size_t(4) << 20;   /* 4 Mi BF16 = 8 MiB */
+static __device__ __align__(256) uint16_t g_noalloc_scratch[kNoAllocScratchElements];
+
+constexpr int kNoAllocMaxDevices = 64;
+static uint16_t *g_noalloc_scratch_address[kNoAllocMaxDevices] = {nullptr};
+
+/* `g_noalloc_scratch` named in host code is only a handle for the runtime, not a device
+ * address; the address is looked up once per device, with that device current. */
+static uint16_t *noalloc_scratch_for(h3_gpu *gpu) {
+    int current = -1;
+    cudaError_t status = cudaGetDevice(&current);
+    if (status != cudaSuccess) {
+        h3b_fail_cuda(gpu, "cudaGetDevice", status);
+        return nullptr;
+    }
+    if (current != gpu->device || current < 0 || current >= kNoAllocMaxDevices) {
+        h3b_fail(gpu, "the context's device %d is not the calling thread's current device %d",
+                 gpu->device, current);
+        return nullptr;
+    }
+    if (!g_noalloc_scratch_address[current]) {
+        void *address = nullptr;
+        status = cudaGetSymbolAddress(&address, g_noalloc_scratch);
+        if (status != cudaSuccess || !address) {
+            h3b_fail_cuda(gpu, "cudaGetSymbolAddress(no-allocation scratch)", status);
+            return nullptr;
+        }
+        g_noalloc_scratch_address[current] = static_cast<uint16_t *>(address);
+    }
+    return g_noalloc_scratch_address[current];
+}
+
+extern "C" int h3x_adaln_linear_bf16_noalloc(h3_gpu *gpu, h3_gpu_tensor *output,
+                                             h3_gpu_tensor *inverse, const h3_gpu_tensor *input,
+                                             size_t input_offset,
+                                             const h3_gpu_tensor *norm_weight,
+                                             const h3_gpu_tensor *modulation,
+                                             const h3_gpu_tensor *row_map,
+                                             const h3_gpu_tensor *weight,
+                                             const h3_gpu_tensor *bias, uint32_t rows,
+                                             uint32_t width, uint32_t output_dim, uint32_t slots,
+                                             uint32_t shift_slot, uint32_t scale_slot,
+                                             float epsilon) {
+    if (!gpu) return 0;
+    size_t in_count = size_t(rows) * width;
+    if (in_count > kNoAllocScratchElements)
+        return h3b_fail(gpu,
+                        "h3x_adaln_linear_bf16_noalloc: rows * width = %zu exceeds the built-in "
+                        "scratch of %zu elements; use h3_gpu_adaln_linear_bf16 for larger calls",
+                        in_count, kNoAllocScratchElements);
+    if (input_offset > SIZE_MAX - in_count)
+        return h3b_fail(gpu, "fused final head input offset is out of range");
+    if (!h3b_need(gpu, input, H3_GPU_BF16, input_offset + in_count, "fused final head input") ||
+        !h3b_need(gpu, inverse, H3_GPU_F32, rows, "fused final head inverse RMS") ||
+        !h3b_need(gpu, norm_weight, H3_GPU_BF16, width, "fused final head norm") ||
+        !h3b_need(gpu, modulation, H3_GPU_BF16, 1, "fused final head modulation") ||
+        !h3b_need(gpu, row_map, H3_GPU_U32, rows, "fused final head row map") ||
+        !h3b_need(gpu, weight, H3_GPU_BF16, size_t(output_dim) * width, "fused final head weight") ||
+        !h3b_need(gpu, output, H3_GPU_BF16, size_t(rows) * output_dim, "fused final head output") ||
+        (bias && !h3b_need(gpu, bias, H3_GPU_BF16, output_dim, "fused final head bias")) ||
+        !h3b_need_command(gpu))
+        return 0;
+    if (shift_slot >= slots || scale_slot >= slots)
+        return h3b_fail(gpu, "fused final head modulation slot is out of range");
+    uint16_t *normed = noalloc_scratch_for(gpu);
+    if (!normed) return 0;
+    if (!rows || !width) return h3b_launched(gpu, "adaln_linear_bf16_noalloc");
+    /* every element of the scratch region that the projection reads is written by the
+     * normalisation kernel first, so nothing left over from an earlier call is consumed */
+    RowArgs a = {};
+    a.input = h3b_ptr<uint16_t>(input, input_offset);
+    a.norm = h3b_ptr<uint16_t>(norm_weight);
+    a.norm_mod = h3b_ptr<uint16_t>(modulation);
+    a.row_map = h3b_ptr<uint32_t>(row_map);
+    a.output = normed;
+    a.inverse = h3b_ptr<float>(inverse);
+    a.rows = rows; a.width = width; a.slots = slots;
+    a.shift_slot = shift_slot; a.scale_slot = scale_slot; a.epsilon = epsilon;
+    launch_row<ROW_ADALN_KEEP>(gpu, a);
+    if (!h3b_launched(gpu, "adaln_linear_bf16_noalloc normalisation")) return 0;
+    if (!output_dim) return 1;
+    return h3b_gemm_bf16(gpu, h3b_ptr<uint16_t>(output), normed, h3b_ptr<uint16_t>(weight),
+                         bias ? h3b_ptr<uint16_t>(bias) : nullptr, rows, width, output_dim,
+                         H3B_EPI_STORE, "adaln_linear_bf16_noalloc");
+}
+
 /* ----------------------------------------------------------- elementwise */
 
 template <int OP>

@@ -305,6 +305,39 @@ int h3x_ulysses_unpack_heads(h3_gpu *gpu, h3_gpu_tensor *dst, const h3_gpu_tenso
                              uint32_t rows_local, uint32_t heads, uint32_t head_dim,
                              uint32_t world);
 
+/* Final head (adaLN + projection) for callers that must not allocate device memory.
+ * No counterpart in the reference: its final head always draws its scratch from a
+ * grow-only cudaMalloc'd workspace.
+ *
+ * Who needs this: a host that has handed all device memory to its own pool before the
+ * denoiser runs (a serving process that pre-partitions HBM, so a late cudaMalloc can fail
+ * or stall behind the driver's allocation lock), or that calls from a thread where
+ * driver allocations are forbidden for latency reasons. h3_gpu_adaln_linear_bf16 grows a
+ * cudaMalloc'd workspace on demand; this variant never calls cudaMalloc / cudaFree or any
+ * allocating library routine. The caller still passes every input and output tensor.
+ *
+ * The intermediate (the BF16-rounded adaLN rows, rows * width elements) lives in a fixed
+ * 8 MiB array inside the library image, so rows * width may not exceed 4 Mi elements
+ * (4,194,304; e.g. 780 rows at the model width 5376); larger calls are rejected with a
+ * message and must use h3_gpu_adaln_linear_bf16. Each GPU that loads the library holds
+ * those 8 MiB until the process exits.
+ *
+ * The first call on a device looks up the array's device address (once per device, with
+ * the context's device current on the calling thread); make that first call before any
+ * stream capture begins. All calls on a device share the one array: it keeps the previous
+ * call's contents, which is harmless because every element the projection reads is
+ * rewritten first, but two calls whose kernels overlap on the GPU (different streams or
+ * contexts on the same device) race on it and must be serialised by the caller.
+ * Arguments, results and error behaviour are otherwise those of h3_gpu_adaln_linear_bf16. */
+int h3x_adaln_linear_bf16_noalloc(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *inverse,
+                                  const h3_gpu_tensor *input, size_t input_offset,
+                                  const h3_gpu_tensor *norm_weight,
+                                  const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map,
+                                  const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                                  uint32_t rows, uint32_t width, uint32_t output_dim,
+                                  uint32_t slots, uint32_t shift_slot, uint32_t scale_slot,
+                                  float epsilon);
+
 #ifdef __cplusplus
 }
 #endif
