@@ -3,24 +3,30 @@
  * behind the same C ABI.
  *
  * Flash attention on the 5th-generation tensor cores (head_dim 128):
- *   grid = (ceil(S/128) query tiles, heads); two CTAs share an SM, so one CTA's
- *   softmax overlaps the other's matrix work.
- *   warp 0     TMA producer: Q tile once, then K/V tiles of 64 keys into a
- *              2-stage ring (3-D tensor maps over [row][head][128], 128-byte
- *              swizzle; rows past S are zero-filled by the copy engine).
- *   warp 1     one thread issues tcgen05.mma: S_j = Q.K_j^T (M128 N64 K128)
- *              into one of two TMEM score buffers, and O += P_j.V_j
- *              (M128 N128 K64, V read as an N-major operand) into a TMEM
- *              accumulator.
- *   warps 2-5  softmax, one query row per thread: read S_j from TMEM, online
- *              max/sum in the exp2 domain, round P to BF16 (the reference's
- *              rounding point before P.V, h3_cuda_attention.cu:1526-1528) and
- *              write it to shared memory in the swizzled K-major layout the
- *              tensor core reads. The running maximum is only raised when it
- *              would grow by more than 2^8, in which case the thread rescales
- *              its O row in TMEM; results are exact either way because the row
- *              sum uses the same maximum.
- *   Every wait is bounded (status H3B_STATUS_ATTN_TIMEOUT, reported by submit).
+ *   grid = (ceil(S/256), heads); one CTA per SM works on two 128-row query tiles that
+ *   ping-pong: while one tile's softmax runs, the tensor core works for the other, and every
+ *   K/V tile fetched into shared memory is used by both.
+ *   warp 0      TMA producer: the 256 query rows once, then K tiles (3-stage ring) and V
+ *               tiles (2-stage ring) of 128 keys (3-D tensor maps over [row][head][128],
+ *               128-byte swizzle; rows past S are zero-filled by the copy engine).
+ *   warp 1      issues tcgen05.mma (all lanes run the loop so operands stay warp-uniform,
+ *               lane 0 issues): S_t = Q_t.K_j^T (M128 N128 K16 x 8, both operands in smem)
+ *               into the tile's TMEM score buffer, and O_t += P_j.V_j (M128 N128 K16 x 8)
+ *               with P read from TENSOR MEMORY as the A operand and V as an N-major smem
+ *               operand. P_t overwrites the first half of S_t; the next Q.K^T of the tile
+ *               is issued right behind P.V, in-order execution protects P.
+ *               128-key tiles keep every instruction at N=128: measured here, N=64
+ *               instructions reach only ~75 % of the N=128 rate.
+ *   warps 2-17  softmax: per query tile 4 lane quarters x 2 key halves. A thread owns one
+ *               query row (its TMEM lane) and 64 keys: scores TMEM -> registers, maxima of
+ *               the two halves exchanged through shared memory (named barrier of the two
+ *               warps), online max/sum in the exp2 domain (ex2.approx), P rounded to BF16
+ *               (the reference's rounding point before P.V, h3_cuda_attention.cu:1526-1528)
+ *               and stored to TMEM. The running maximum is raised lazily (only when it
+ *               would grow by more than 2^8) with an in-TMEM rescale of O; results are exact
+ *               either way because the row sum uses the same maximum.
+ *   Every wait is bounded (status H3B_STATUS_ATTN_TIMEOUT, reported by submit); the
+ *   named barrier of a warp pair also carries a "still running" vote so both leave together.
  *
  * A SIMT flash kernel serves other head sizes (the reference's small test
  * shapes); it follows the same online-softmax recurrence in F32.
@@ -254,20 +260,31 @@ h3b_sdpa_simt(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t 
 
 /* ------------------------------------------- tensor-core flash attention */
 
-constexpr int AT_Q = 128;               /* query rows per CTA            */
-constexpr int AT_KV = 64;               /* keys per tile                 */
+constexpr int AT_QT = 128;              /* rows of one query tile        */
+constexpr int AT_TILES = 2;             /* query tiles per CTA           */
+constexpr int AT_Q = AT_QT * AT_TILES;  /* query rows per CTA            */
+constexpr int AT_KV = 128;              /* keys per tile                 */
 constexpr int AT_D = 128;               /* head dim                      */
-constexpr int AT_STAGES = 2;
-constexpr int AT_THREADS = 192;
-constexpr int AT_Q_BYTES = AT_Q * AT_D * 2;      /* 32 KiB: two 64-column boxes */
-constexpr int AT_K_BYTES = AT_KV * AT_D * 2;     /* 16 KiB: two boxes           */
-constexpr int AT_V_BYTES = AT_KV * AT_D * 2;     /* 16 KiB: two boxes           */
-constexpr int AT_P_BYTES = AT_Q * AT_KV * 2;     /* 16 KiB: one box             */
-constexpr int AT_STAGE_BYTES = AT_K_BYTES + AT_V_BYTES;
-constexpr int AT_BAR_BYTES = 128;
-constexpr size_t AT_SMEM = AT_Q_BYTES + AT_STAGES * AT_STAGE_BYTES + AT_P_BYTES + AT_BAR_BYTES;
-constexpr uint32_t AT_TMEM_COLS = 256;           /* S0 64 | S1 64 | O 128       */
-constexpr float AT_RESCALE_THRESHOLD = 8.0f;     /* log2 units                  */
+constexpr int AT_K_STAGES = 3;
+constexpr int AT_V_STAGES = 2;
+constexpr int AT_SOFTMAX_WARPS = 8 * AT_TILES;   /* per tile: 4 lane quarters x 2 key halves */
+constexpr int AT_THREADS = 64 + 32 * AT_SOFTMAX_WARPS;  /* producer, MMA, softmax warps */
+constexpr int AT_Q_BYTES = AT_Q * AT_D * 2;      /* 64 KiB: two boxes of [256 rows][64 dims] */
+constexpr int AT_K_BYTES = AT_KV * AT_D * 2;     /* 32 KiB: two boxes of [128 keys][64 dims] */
+constexpr int AT_V_BYTES = AT_KV * AT_D * 2;     /* 32 KiB: two boxes                        */
+constexpr int AT_BAR_BYTES = 256;
+constexpr int AT_XCHG_BYTES = AT_TILES * 2 * AT_QT * 4;   /* row maxima / sums between key halves */
+constexpr size_t AT_SMEM =
+    AT_Q_BYTES + AT_K_STAGES * AT_K_BYTES + AT_V_STAGES * AT_V_BYTES + AT_BAR_BYTES + AT_XCHG_BYTES;
+/* Tensor-memory columns (32-bit each, 128 lanes = query rows):
+ *   [  0,256)  S_t scores F32 (128 columns per query tile); P_t (BF16 pairs, 64 columns)
+ *              overwrites the first half of S_t and is the A operand of P.V
+ *   [256,512)  O_t accumulators F32 (128 columns per tile)
+ * Keys are taken 128 at a time so that every tcgen05.mma is M128 N128 K16: measured on
+ * B200, N=64 instructions run at well under the N=128 rate.                          */
+constexpr uint32_t AT_TMEM_COLS = 512;
+constexpr uint32_t AT_COL_S = 0, AT_COL_O = 256;
+constexpr float AT_RESCALE_THRESHOLD = 8.0f;     /* log2 units */
 
 struct AttnArgs {
     uint16_t *out;
@@ -275,7 +292,16 @@ struct AttnArgs {
     uint32_t seq, heads;
     float scale_log2;
     int head_major;
+    long long *trace;   /* optional [role][tile][event] clock64 stamps of CTA (0,0); NULL = off */
 };
+
+/* Development aid: when args.trace is set, CTA (0,0) records clock64() at the phase
+ * boundaries of its first 32 key tiles. */
+#define AT_TRACE(role, j, ev)                                                          \
+    do {                                                                               \
+        if (args.trace && blockIdx.x == 0 && blockIdx.y == 0 && (j) < 32 && lane == 0) \
+            args.trace[((role) * 32 + (j)) * 8 + (ev)] = clock64();                    \
+    } while (0)
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int x, int y, int z) {
@@ -309,41 +335,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-/* N-major (MN-major) B operand: V tile [64 keys][128 dims] held as two boxes of
- * [64 keys][64 dims] with 128-byte swizzle. Along N, 64-element groups are one
- * box (8192 bytes) apart = leading byte offset; along K, groups of 8 keys are
- * 1024 bytes apart = stride byte offset. */
-__device__ __forceinline__ uint64_t v_operand_desc(uint32_t smem_addr) {
-    uint64_t desc = (smem_addr >> 4) & 0x3fffu;
-    desc |= uint64_t(8192 >> 4) << 16;
-    desc |= uint64_t(1024 >> 4) << 32;
-    desc |= uint64_t(1) << 46;
-    desc |= uint64_t(2) << 61;
-    return desc;
-}
-
-__global__ void __launch_bounds__(AT_THREADS, 2)
+/* V tile [128 keys][128 dims] is held as two boxes of [128 keys][64 dims] with 128-byte
+ * swizzle and read as an N-major B operand: along N, 64-element groups are one box
+ * (16384 bytes) apart = leading byte offset; along K, groups of 8 keys are 1024 bytes
+ * apart = stride byte offset; 16 keys (one instruction) are 2048 bytes. */
+__global__ void __launch_bounds__(AT_THREADS, 1)
 h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
     extern __shared__ __align__(1024) uint8_t at_smem[];
     const uint32_t base = smem_u32(at_smem);
     const uint32_t q_smem = base;
-    const uint32_t kv_smem = q_smem + AT_Q_BYTES;
-    const uint32_t p_smem = kv_smem + AT_STAGES * AT_STAGE_BYTES;
-    const uint32_t bars = p_smem + AT_P_BYTES;
-    const uint32_t q_full = bars;
-    const uint32_t k_full = bars + 8;                  /* 2 */
-    const uint32_t v_full = bars + 24;                 /* 2 */
-    const uint32_t kv_empty = bars + 40;               /* 2 */
-    const uint32_t s_full = bars + 56;                 /* 2 */
-    const uint32_t s_empty = bars + 72;                /* 2 */
-    const uint32_t p_full = bars + 88;
-    const uint32_t pv_done = bars + 96;
-    const uint32_t tmem_holder = bars + 104;
-    volatile int *stop = reinterpret_cast<volatile int *>(at_smem + (bars - base) + 112);
+    const uint32_t k_smem = q_smem + AT_Q_BYTES;
+    const uint32_t v_smem = k_smem + AT_K_STAGES * AT_K_BYTES;
+    const uint32_t bars = v_smem + AT_V_STAGES * AT_V_BYTES;
+    const uint32_t q_full = bars;                          /* 1           */
+    const uint32_t k_full = bars + 8;                      /* AT_K_STAGES */
+    const uint32_t k_empty = k_full + 8 * AT_K_STAGES;     /* AT_K_STAGES */
+    const uint32_t v_full = k_empty + 8 * AT_K_STAGES;     /* AT_V_STAGES */
+    const uint32_t v_empty = v_full + 8 * AT_V_STAGES;     /* AT_V_STAGES */
+    const uint32_t s_full = v_empty + 8 * AT_V_STAGES;     /* [tile] = 2  */
+    const uint32_t p_full = s_full + 16;                   /* [tile] = 2  */
+    const uint32_t o_done = p_full + 16;                   /* 1           */
+    const uint32_t tmem_holder = o_done + 8;
+    volatile int *stop = reinterpret_cast<volatile int *>(at_smem + (tmem_holder + 8 - base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_tile = blockIdx.x, head = blockIdx.y;
+    const uint32_t q_block = blockIdx.x, head = blockIdx.y;
     const uint32_t n_tiles = (args.seq + AT_KV - 1) / AT_KV;
 
     if ((base & 1023u) != 0) {  /* swizzled tiles need 1024-byte alignment */
@@ -353,15 +370,19 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     if (threadIdx.x == 0) {
         *stop = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < AT_K_STAGES; s++) {
             mbar_init(k_full + 8 * s, 1);
-            mbar_init(v_full + 8 * s, 1);
-            mbar_init(kv_empty + 8 * s, 1);
-            mbar_init(s_full + 8 * s, 1);
-            mbar_init(s_empty + 8 * s, 4);
+            mbar_init(k_empty + 8 * s, 1);
         }
-        mbar_init(p_full, 4);
-        mbar_init(pv_done, 1);
+        for (int s = 0; s < AT_V_STAGES; s++) {
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
+        }
+        for (int t = 0; t < AT_TILES; t++) {
+            mbar_init(s_full + 8 * t, 1);
+            mbar_init(p_full + 8 * t, 8);
+        }
+        mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -373,100 +394,176 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
-    const uint32_t tmem_o = tmem_base + 128;
 
     if (warp == 0) {
         /* ------------------------------------------------ TMA producer */
         if (lane == 0) {
             mbar_expect_tx(q_full, AT_Q_BYTES);
-            tma_load_3d(q_smem, &map_q, q_full, 0, int(head), int(q_tile * AT_Q));
-            tma_load_3d(q_smem + AT_Q_BYTES / 2, &map_q, q_full, 64, int(head), int(q_tile * AT_Q));
+            tma_load_3d(q_smem, &map_q, q_full, 0, int(head), int(q_block * AT_Q));
+            tma_load_3d(q_smem + AT_Q_BYTES / 2, &map_q, q_full, 64, int(head), int(q_block * AT_Q));
+            uint32_t ks = 0, kp = 0, vs = 0, vp = 0;
             for (uint32_t j = 0; j < n_tiles; j++) {
-                const uint32_t stage = j & 1, round = j >> 1;
-                if (!mbar_wait(kv_empty + 8 * stage, (round & 1) ^ 1, stop)) break;
-                const uint32_t k_dst = kv_smem + stage * AT_STAGE_BYTES;
-                const uint32_t v_dst = k_dst + AT_K_BYTES;
                 const int row0 = int(j * AT_KV);
-                mbar_expect_tx(k_full + 8 * stage, AT_K_BYTES);
-                tma_load_3d(k_dst, &map_k, k_full + 8 * stage, 0, int(head), row0);
-                tma_load_3d(k_dst + AT_K_BYTES / 2, &map_k, k_full + 8 * stage, 64, int(head), row0);
-                mbar_expect_tx(v_full + 8 * stage, AT_V_BYTES);
-                tma_load_3d(v_dst, &map_v, v_full + 8 * stage, 0, int(head), row0);
-                tma_load_3d(v_dst + AT_V_BYTES / 2, &map_v, v_full + 8 * stage, 64, int(head), row0);
+                if (!mbar_wait(k_empty + 8 * ks, kp ^ 1, stop)) break;
+                mbar_expect_tx(k_full + 8 * ks, AT_K_BYTES);
+                tma_load_3d(k_smem + ks * AT_K_BYTES, &map_k, k_full + 8 * ks, 0, int(head), row0);
+                tma_load_3d(k_smem + ks * AT_K_BYTES + AT_K_BYTES / 2, &map_k, k_full + 8 * ks, 64,
+                            int(head), row0);
+                if (++ks == AT_K_STAGES) { ks = 0; kp ^= 1; }
+                if (!mbar_wait(v_empty + 8 * vs, vp ^ 1, stop)) break;
+                mbar_expect_tx(v_full + 8 * vs, AT_V_BYTES);
+                tma_load_3d(v_smem + vs * AT_V_BYTES, &map_v, v_full + 8 * vs, 0, int(head), row0);
+                tma_load_3d(v_smem + vs * AT_V_BYTES + AT_V_BYTES / 2, &map_v, v_full + 8 * vs, 64,
+                            int(head), row0);
+                if (++vs == AT_V_STAGES) { vs = 0; vp ^= 1; }
             }
         }
     } else if (warp == 1) {
         /* -------------------------------------------------- MMA issuer */
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = instruction_desc(AT_Q, AT_KV);
-            constexpr uint32_t idesc_pv = instruction_desc(AT_Q, AT_D) | (1u << 16); /* B N-major */
-            bool alive = mbar_wait(q_full, 0, stop);
-            auto issue_qk = [&](uint32_t j) -> bool {
-                const uint32_t stage = j & 1, round = j >> 1;
-                if (!mbar_wait(k_full + 8 * stage, round & 1, stop)) return false;
-                if (!mbar_wait(s_empty + 8 * stage, (round & 1) ^ 1, stop)) return false;
-                tc_fence_after();
-                const uint32_t k_src = kv_smem + stage * AT_STAGE_BYTES;
+        /* all 32 lanes run the loop (warp-uniform control flow and operands); lane 0 issues */
+        {
+            const uint32_t leader = lane == 0;
+            constexpr uint32_t idesc_qk = instruction_desc(AT_QT, AT_KV);
+            constexpr uint32_t idesc_pv = instruction_desc(AT_QT, AT_D) | (1u << 16); /* B N-major */
+            const uint32_t q_lo0 = desc_lo_kmajor(q_smem);
+            const uint32_t k_lo0 = desc_lo_kmajor(k_smem);
+            const uint32_t v_lo0 = desc_lo_nmajor(v_smem, AT_V_BYTES / 2);
+            /* S_t = Q_t . K_j^T : Q box b holds dims [64b, 64b+64) of all 256 rows, tile t starts
+             * 16 KiB into the box; K likewise in two boxes; 32 bytes per 16-dim slice */
+            auto issue_qk = [&](uint32_t t, uint32_t k_lo) {
+                const uint32_t d = tmem_base + AT_COL_S + t * AT_KV;
+                const uint32_t a_lo = q_lo0 + t * ((AT_QT * 128) >> 4);
+                umma_ss<false>(d, a_lo, k_lo, idesc_qk, leader);
 #pragma unroll
-                for (int kk = 0; kk < AT_D / 16; kk++) {
-                    const uint64_t a = operand_desc(q_smem + (kk >> 2) * (AT_Q_BYTES / 2)) +
-                                       uint64_t(2 * (kk & 3));
-                    const uint64_t b = operand_desc(k_src + (kk >> 2) * (AT_K_BYTES / 2)) +
-                                       uint64_t(2 * (kk & 3));
-                    umma_bf16(tmem_base + stage * AT_KV, a, b, idesc_qk, kk != 0);
-                }
-                umma_commit(s_full + 8 * stage);
-                return true;
+                for (int kk = 1; kk < AT_D / 16; kk++)
+                    umma_ss<true>(d, a_lo + (kk >> 2) * ((AT_Q_BYTES / 2) >> 4) + 2 * (kk & 3),
+                                  k_lo + (kk >> 2) * ((AT_K_BYTES / 2) >> 4) + 2 * (kk & 3), idesc_qk,
+                                  leader);
+                umma_commit_if(s_full + 8 * t, leader);
             };
-            if (alive) alive = issue_qk(0);
-            for (uint32_t j = 0; alive && j < n_tiles; j++) {
-                if (j + 1 < n_tiles && !issue_qk(j + 1)) break;
-                const uint32_t stage = j & 1, round = j >> 1;
-                if (!mbar_wait(p_full, j & 1, stop)) break;
-                if (!mbar_wait(v_full + 8 * stage, round & 1, stop)) break;
+            bool alive = mbar_wait(q_full, 0, stop) && mbar_wait(k_full, 0, stop);
+            alive = __all_sync(0xffffffffu, alive);
+            if (alive) {
                 tc_fence_after();
-                const uint32_t v_src = kv_smem + stage * AT_STAGE_BYTES + AT_K_BYTES;
-#pragma unroll
-                for (int kk = 0; kk < AT_KV / 16; kk++) {
-                    const uint64_t a = operand_desc(p_smem) + uint64_t(2 * kk);
-                    const uint64_t b = v_operand_desc(v_src + kk * 16 * 128);
-                    umma_bf16(tmem_o, a, b, idesc_pv, (j | uint32_t(kk)) != 0);
-                }
-                umma_commit(pv_done);
-                umma_commit(kv_empty + 8 * stage);
+                issue_qk(0, k_lo0);
+                issue_qk(1, k_lo0);
+                umma_commit_if(k_empty, leader);
             }
+            uint32_t ks = 1 % AT_K_STAGES, kp = (AT_K_STAGES == 1), vs = 0, vp = 0;
+            for (uint32_t j = 0; alive && j < n_tiles; j++) {
+                const uint32_t v_lo = v_lo0 + vs * (AT_V_BYTES >> 4);
+                const uint32_t k_lo_next = k_lo0 + ks * (AT_K_BYTES >> 4);
+                const bool more = j + 1 < n_tiles;
+                AT_TRACE(0, j, 0);
+#pragma unroll
+                for (int t = 0; t < AT_TILES; t++) {
+                    alive = __all_sync(0xffffffffu, mbar_wait(p_full + 8 * t, j & 1, stop));
+                    if (alive && t == 0)
+                        alive = __all_sync(0xffffffffu, mbar_wait(v_full + 8 * vs, vp, stop));
+                    if (!alive) break;
+                    AT_TRACE(0, j, 1 + 2 * t);
+                    tc_fence_after();
+                    /* O_t += P_t . V_j : A = P_t in TMEM (first 64 columns of S_t), 8 columns and
+                     * 2048 bytes of V per 16 keys */
+                    const uint32_t d = tmem_base + AT_COL_O + t * AT_D;
+                    const uint32_t a = tmem_base + AT_COL_S + t * AT_KV;
+                    if (j == 0) umma_ts<false>(d, a, v_lo, idesc_pv, leader);
+                    else umma_ts<true>(d, a, v_lo, idesc_pv, leader);
+#pragma unroll
+                    for (int kk = 1; kk < AT_KV / 16; kk++)
+                        umma_ts<true>(d, a + kk * 8, v_lo + kk * (2048 >> 4), idesc_pv, leader);
+                    if (t == AT_TILES - 1) umma_commit_if(v_empty + 8 * vs, leader);
+                    if (more) {
+                        /* the next scores of this tile go straight behind: in-order execution keeps
+                         * them from overwriting P_t before P_t.V_j has read it */
+                        if (t == 0) {
+                            alive = __all_sync(0xffffffffu, mbar_wait(k_full + 8 * ks, kp, stop));
+                            if (!alive) break;
+                            tc_fence_after();
+                        }
+                        issue_qk(t, k_lo_next);
+                        if (t == AT_TILES - 1) umma_commit_if(k_empty + 8 * ks, leader);
+                    }
+                    AT_TRACE(0, j, 2 + 2 * t);
+                }
+                if (!alive) break;
+                if (++vs == AT_V_STAGES) { vs = 0; vp ^= 1; }
+                if (++ks == AT_K_STAGES) { ks = 0; kp ^= 1; }
+            }
+            if (alive) umma_commit_if(o_done, leader);
         }
     } else {
         /* ------------------------------------------------------ softmax */
+        /* 16 warps: query tile (2) x key half (2) x lane quarter (4). A thread owns one query
+         * row (its TMEM lane) and 64 of the 128 keys of a tile; the two warps that share a
+         * row exchange their maxima through shared memory, so both use the same reference
+         * maximum, and keep separate partial row sums that are added at the end. */
+        const uint32_t idx = uint32_t(warp - 2);
+        const uint32_t tile = idx >> 3, half = (idx >> 2) & 1u;
         const uint32_t quarter = warp & 3;
         const uint32_t local_row = quarter * 32 + lane;
-        const uint32_t row = q_tile * AT_Q + local_row;
+        const uint32_t row = q_block * AT_Q + tile * AT_QT + local_row;
         const uint32_t lane_base = (quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_base + AT_COL_S + tile * AT_KV + half * 64 + lane_base;
+        const uint32_t tmem_p = tmem_base + AT_COL_S + tile * AT_KV + half * 32 + lane_base;
+        const uint32_t tmem_o = tmem_base + AT_COL_O + tile * AT_D + lane_base;
+        const uint32_t my_s_full = s_full + 8 * tile, my_p_full = p_full + 8 * tile;
+        const uint32_t pair_barrier = 1 + tile * 4 + quarter;          /* 64 threads each */
+        float *xchg = reinterpret_cast<float *>(at_smem + (bars - base) + AT_BAR_BYTES);
+        float *mine = xchg + (tile * 2 + half) * AT_QT + local_row;
+        const float *theirs = xchg + (tile * 2 + (half ^ 1u)) * AT_QT + local_row;
+        const float scale_log2 = args.scale_log2;
+
         float m_run = -INFINITY, l_run = 0.0f;
         bool alive = true;
         for (uint32_t j = 0; alive && j < n_tiles; j++) {
-            const uint32_t buf = j & 1, round = j >> 1;
-            if (!mbar_wait(s_full + 8 * buf, round & 1, stop)) { alive = false; break; }
+            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 0);
+            /* S_t(j) complete; every earlier MMA of this CTA (P.V of tile j-1 included) too */
+            const bool ready = __all_sync(0xffffffffu, mbar_wait(my_s_full, j & 1, stop));
+            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 1);
             tc_fence_after();
+            /* the loads run even if the wait gave up (tensor-memory reads are always safe), so
+             * the score registers have one definition and stay in registers */
             uint32_t s0[32], s1[32];
-            tmem_ld32(tmem_base + lane_base + buf * AT_KV, s0);
-            tmem_ld32(tmem_base + lane_base + buf * AT_KV + 32, s1);
+            tmem_ld32(tmem_s, s0);
+            tmem_ld32(tmem_s + 32, s1);
             tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty + 8 * buf);
-
-            const uint32_t valid = args.seq - j * AT_KV;   /* >= 1; >= 64 except on the last tile */
-            float tile_max = -INFINITY;
+            const uint32_t valid = args.seq - j * AT_KV;   /* >= 1; < 128 only on the last tile */
+            if (valid < uint32_t(AT_KV)) {
+                const uint32_t k0 = half * 64;
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                float a = uint32_t(i) < valid ? __uint_as_float(s0[i]) : -INFINITY;
-                float b = uint32_t(i + 32) < valid ? __uint_as_float(s1[i]) : -INFINITY;
-                s0[i] = __float_as_uint(a);
-                s1[i] = __float_as_uint(b);
-                tile_max = fmaxf(tile_max, fmaxf(a, b));
+                for (int i = 0; i < 32; i++) {
+                    if (k0 + i >= valid) s0[i] = 0xff800000u;        /* -inf */
+                    if (k0 + 32 + i >= valid) s1[i] = 0xff800000u;
+                }
             }
-            const float m_tile = tile_max * args.scale_log2;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(s0[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(s1[i]));
+                mx3 = fmaxf(mx3, __uint_as_float(s1[i + 1]));
+            }
+            const float mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            *mine = mx_half;
+            /* Pair barrier: after it both key halves have their scores in registers (P may
+             * overwrite S) and see each other's maximum. It also carries the "still running"
+             * vote, so the two warps of a row always leave the loop in the same iteration. */
+            {
+                uint32_t both;
+                asm volatile(
+                    "{\n\t.reg .pred pin, pout;\n\t"
+                    "setp.ne.u32 pin, %2, 0;\n\t"
+                    "bar.red.and.pred pout, %1, 64, pin;\n\t"
+                    "selp.u32 %0, 1, 0, pout;\n\t}"
+                    : "=r"(both)
+                    : "r"(pair_barrier), "r"(uint32_t(ready))
+                    : "memory");
+                if (!both) { alive = false; break; }
+            }
+            const float m_tile = fmaxf(mx_half, *theirs) * scale_log2;
+            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 2);
             float alpha = 1.0f;
             bool rescale = false;
             if (m_tile - m_run > AT_RESCALE_THRESHOLD) {   /* also true on the first tile */
@@ -474,63 +571,59 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 m_run = m_tile;
                 rescale = true;
             }
-            float tile_sum = 0.0f;
+            const float neg_m = -m_run;
+            float sum0 = 0.0f, sum1 = 0.0f;
             uint32_t packed[32];
 #pragma unroll
             for (int i = 0; i < 16; i++) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(s0[2 * i]), args.scale_log2, -m_run));
-                float p1 = fast_exp2(fmaf(__uint_as_float(s0[2 * i + 1]), args.scale_log2, -m_run));
-                float p2 = fast_exp2(fmaf(__uint_as_float(s1[2 * i]), args.scale_log2, -m_run));
-                float p3 = fast_exp2(fmaf(__uint_as_float(s1[2 * i + 1]), args.scale_log2, -m_run));
-                tile_sum += (p0 + p1) + (p2 + p3);
+                float p0 = fast_exp2(fmaf(__uint_as_float(s0[2 * i]), scale_log2, neg_m));
+                float p1 = fast_exp2(fmaf(__uint_as_float(s0[2 * i + 1]), scale_log2, neg_m));
+                float p2 = fast_exp2(fmaf(__uint_as_float(s1[2 * i]), scale_log2, neg_m));
+                float p3 = fast_exp2(fmaf(__uint_as_float(s1[2 * i + 1]), scale_log2, neg_m));
+                sum0 += p0 + p1;
+                sum1 += p2 + p3;
                 packed[i] = pack_bf16(p0, p1);
                 packed[16 + i] = pack_bf16(p2, p3);
             }
-            l_run = l_run * alpha + tile_sum;
+            l_run = l_run * alpha + (sum0 + sum1);
+            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 3);
 
-            if (j > 0) {
-                /* P buffer free and O stable once P_{j-1}.V_{j-1} has finished */
-                if (!mbar_wait(pv_done, (j - 1) & 1, stop)) { alive = false; break; }
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, rescale)) {
+            if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+                /* O_t is stable: P.V of tile j-1 finished before S_t(j) was signalled. Each
+                 * key half rescales its own 64 columns of O_t (the decision is identical in
+                 * both warps of a row: same maxima, same history). */
 #pragma unroll 1
-                    for (int c = 0; c < AT_D / 32; c++) {
-                        uint32_t o[32];
-                        tmem_ld32(tmem_o + lane_base + c * 32, o);
-                        tmem_ld_wait();
+                for (int c = 0; c < 2; c++) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + half * 64 + c * 32, o);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tmem_o + lane_base + c * 32, o);
-                    }
-                    tmem_st_wait();
+                    for (int i = 0; i < 32; i++)
+                        o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tmem_o + half * 64 + c * 32, o);
                 }
             }
-            /* P row: 64 BF16 = 8 chunks of 16 bytes, chunk c of row r at ((c ^ (r & 7)) << 4) */
-            const uint32_t p_row = p_smem + local_row * 128;
-#pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const uint32_t addr = p_row + ((uint32_t(c) ^ (local_row & 7u)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                             "r"(packed[4 * c]), "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]),
-                             "r"(packed[4 * c + 3])
-                             : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            /* keys 64*half + 2i, +1 -> P column 32*half + i */
+            tmem_st32(tmem_p, packed);
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(my_p_full);
+            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 4);
         }
-        if (alive && mbar_wait(pv_done, (n_tiles - 1) & 1, stop)) {
+        /* total row sum = sum of the two halves' partial sums (same reference maximum) */
+        if (alive) *mine = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+        if (alive && mbar_wait(o_done, 0, stop)) {
             tc_fence_after();
-            const float inv = 1.0f / l_run;
-            uint16_t *dst = args.head_major
-                                ? args.out + (size_t(head) * args.seq + row) * AT_D
-                                : args.out + (size_t(row) * args.heads + head) * AT_D;
+            const float inv = 1.0f / (l_run + *theirs);
+            uint16_t *dst = (args.head_major
+                                 ? args.out + (size_t(head) * args.seq + row) * AT_D
+                                 : args.out + (size_t(row) * args.heads + head) * AT_D) + half * 64;
 #pragma unroll 1
-            for (int c = 0; c < AT_D / 32; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + lane_base + c * 32, o);
+                tmem_ld32(tmem_o + half * 64 + c * 32, o);
                 tmem_ld_wait();
                 if (row < args.seq) {
 #pragma unroll
@@ -614,6 +707,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         args.heads = heads;
         args.scale_log2 = scale * 1.4426950408889634f;
         args.head_major = head_major;
+        args.trace = nullptr;
+        if (const char *t = getenv("H3B_ATTN_TRACE_PTR")) args.trace = reinterpret_cast<long long *>(strtoull(t, nullptr, 0));
         dim3 grid((seq + AT_Q - 1) / AT_Q, heads);
         h3b_sdpa_tc<<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
         return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
@@ -708,6 +803,38 @@ extern "C" int h3_gpu_grouped_qkv_linear_rope_bf16(
     const h3_gpu_tensor *rope_sin, uint32_t rows, uint32_t input_dim, uint32_t heads,
     uint32_t head_dim, uint32_t rope_half, float epsilon) {
     uint32_t inner = heads * head_dim;
+    /* Fused route: the projection's epilogue applies the head norm and RoPE and writes
+     * query/key/value directly; the caller's qkv scratch is then left untouched (the
+     * reference documents it as scratch that a backend may bypass, h3_gpu.h:465-467).
+     * Statistics: one projection + one hand kernel, as the two-step route counts. */
+    if (head_dim == 128 && rope_half == 48 && rows && heads) {
+        size_t count = size_t(rows) * inner, rope_count = size_t(rows) * rope_half;
+        if (!h3b_need(gpu, input, H3_GPU_BF16, size_t(rows) * input_dim, "linear input") ||
+            !h3b_need(gpu, weight, H3_GPU_BF16, size_t(inner) * 3 * input_dim, "linear weight") ||
+            !h3b_need(gpu, qkv, H3_GPU_BF16, count * 3, "linear output") ||
+            !h3b_need(gpu, q_norm, H3_GPU_BF16, head_dim, "Q norm") ||
+            !h3b_need(gpu, k_norm, H3_GPU_BF16, head_dim, "K norm") ||
+            !h3b_need(gpu, rope_cos, H3_GPU_BF16, rope_count, "RoPE cosine") ||
+            !h3b_need(gpu, rope_sin, H3_GPU_BF16, rope_count, "RoPE sine") ||
+            !h3b_need(gpu, query, H3_GPU_BF16, count, "query") ||
+            !h3b_need(gpu, key, H3_GPU_BF16, count, "key") ||
+            !h3b_need(gpu, value, H3_GPU_BF16, count, "value") || !h3b_need_command(gpu))
+            return 0;
+        int fused = h3b_qkv_rope_gemm(gpu, h3b_ptr<uint16_t>(query), h3b_ptr<uint16_t>(key),
+                                      h3b_ptr<uint16_t>(value), h3b_ptr<uint16_t>(input),
+                                      h3b_ptr<uint16_t>(weight), h3b_ptr<uint16_t>(q_norm),
+                                      h3b_ptr<uint16_t>(k_norm), h3b_ptr<uint16_t>(rope_cos),
+                                      h3b_ptr<uint16_t>(rope_sin), rows, input_dim, heads, epsilon);
+        if (fused == 1) {
+            gpu->stats.direct_dispatches++;
+            if (!(rows >= 32 && input_dim >= 256 && inner * 3 >= 256)) {
+                gpu->stats.mps_linear_dispatches--;
+                gpu->stats.direct_dispatches++;
+            }
+            return 1;
+        }
+        if (fused == 0) return 0;
+    }
     return h3_gpu_linear_bf16(gpu, qkv, input, weight, nullptr, rows, input_dim, inner * 3) &&
            h3_gpu_grouped_qkv_rope_bf16(gpu, query, key, value, qkv, q_norm, k_norm, rope_cos,
                                         rope_sin, rows, heads, head_dim, rope_half, epsilon);

@@ -161,7 +161,15 @@ __device__ __forceinline__ float h3b_warp_sum(float v) {
 enum h3b_gemm_epilogue {
     H3B_EPI_STORE = 0,    /* out[r][c] = bf16(acc + bias[c])                          */
     H3B_EPI_SWIGLU = 1,   /* W = [gate rows | up rows]; out[r][c] = swiglu, n = hidden */
+    H3B_EPI_QKV_ROPE = 2, /* grouped QKV: per-head RMSNorm + RoPE, writes q/k/v directly   */
 };
+/* Fused QKV projection + per-head RMSNorm + RoPE for head_dim 128, rope_half 48, grouped
+ * layout. Returns -1 when the shape cannot take the fused kernel (caller runs the two-step
+ * route), else 1/0 like every op. */
+int h3b_qkv_rope_gemm(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const uint16_t *x,
+                      const uint16_t *w, const uint16_t *q_norm, const uint16_t *k_norm,
+                      const uint16_t *rope_cos, const uint16_t *rope_sin, uint32_t rows,
+                      uint32_t in_dim, uint32_t heads, float eps);
 int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
                   const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t n,
                   h3b_gemm_epilogue epilogue, const char *what);

@@ -56,7 +56,75 @@ struct TcArgs {
     uint32_t k_blocks;
     uint32_t tiles_m, tiles_n;
     uint32_t up_offset;   /* SwiGLU: weight row of the first up column (= hidden) */
+    /* QKV + norm + RoPE epilogue */
+    uint16_t *q_out, *k_out, *v_out;
+    const uint16_t *q_norm, *k_norm, *rope_cos, *rope_sin;
+    uint32_t heads;
+    float eps;
 };
+
+constexpr int ROPE_HALF = 48;   /* the model's RoPE width (h3_dit.c ROPE_HALF) */
+
+/* One 128-column unit of the grouped QKV row = q, k or v of one head, held by the thread
+ * that owns the row: F32 accumulators -> BF16 (the reference rounds the projection first),
+ * RMSNorm over the 128 values with the head-norm weight, half-pair RoPE on dims [0,96),
+ * BF16 store. Same expression order as the stand-alone kernel. */
+__device__ __forceinline__ void qkv_unit_epilogue(const TcArgs &args, uint32_t lane_addr,
+                                                  uint32_t unit, uint32_t row, bool row_ok) {
+    const uint32_t head = unit / 3, kind = unit % 3;
+    uint16_t *dst = (kind == 0 ? args.q_out : kind == 1 ? args.k_out : args.v_out) +
+                    (size_t(row) * args.heads + head) * 128;
+    float x[128];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) x[c * 32 + i] = round_bf16(__uint_as_float(r[i]));
+    }
+    if (kind != 2) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 128; i++) ss = fmaf(x[i], x[i], ss);
+        const float inv = 1.0f / sqrtf(ss / 128.0f + args.eps);
+        const uint4 *wsrc = reinterpret_cast<const uint4 *>(kind == 0 ? args.q_norm : args.k_norm);
+#pragma unroll
+        for (int v = 0; v < 16; v++) {
+            const uint4 w = __ldg(wsrc + v);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                x[8 * v + 2 * i] = x[8 * v + 2 * i] * inv * h3b_lo(ww[i]);
+                x[8 * v + 2 * i + 1] = x[8 * v + 2 * i + 1] * inv * h3b_hi(ww[i]);
+            }
+        }
+        const uint32_t trow = row_ok ? row : 0;
+        const uint4 *csrc = reinterpret_cast<const uint4 *>(args.rope_cos + size_t(trow) * ROPE_HALF);
+        const uint4 *ssrc = reinterpret_cast<const uint4 *>(args.rope_sin + size_t(trow) * ROPE_HALF);
+#pragma unroll
+        for (int v = 0; v < ROPE_HALF / 8; v++) {
+            const uint4 c4 = __ldg(csrc + v), s4 = __ldg(ssrc + v);
+            const uint32_t cw[4] = {c4.x, c4.y, c4.z, c4.w}, sw[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int d = 8 * v + i;
+                const float c = (i & 1) ? h3b_hi(cw[i >> 1]) : h3b_lo(cw[i >> 1]);
+                const float s = (i & 1) ? h3b_hi(sw[i >> 1]) : h3b_lo(sw[i >> 1]);
+                const float lo = x[d], hi = x[d + ROPE_HALF];
+                x[d] = lo * c - hi * s;
+                x[d + ROPE_HALF] = hi * c + lo * s;
+            }
+        }
+    }
+    if (row_ok) {
+#pragma unroll
+        for (int v = 0; v < 16; v++)
+            *reinterpret_cast<uint4 *>(dst + v * 8) =
+                make_uint4(pack_bf16(x[8 * v], x[8 * v + 1]), pack_bf16(x[8 * v + 2], x[8 * v + 3]),
+                           pack_bf16(x[8 * v + 4], x[8 * v + 5]), pack_bf16(x[8 * v + 6], x[8 * v + 7]));
+    }
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -139,31 +207,36 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
     } else if (warp == 1) {
-        /* ---- MMA issuer ---- */
-        if (lane == 0) {
+        /* ---- MMA issuer: all lanes run the loop (uniform operands), lane 0 issues ---- */
+        {
+            const uint32_t leader = lane == 0;
             constexpr uint32_t idesc = instruction_desc(BM, BN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
             for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
-                if (!mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop))) break;
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + acc * BN;
                 for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
-                    if (!mbar_wait(full_bar + 8 * stage, phase, stop)) { alive = false; break; }
-                    tc_fence_after();
-                    uint64_t a_desc = operand_desc(a_smem + stage * A_BYTES);
-                    uint64_t b_desc = operand_desc(b_smem + stage * B_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / 16; k++) {
-                        /* 16 BF16 along K = 32 bytes = 2 descriptor address units */
-                        umma_bf16(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), idesc,
-                                  (kb | uint32_t(k)) != 0);
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop))) {
+                        alive = false;
+                        break;
                     }
-                    umma_commit(empty_bar + 8 * stage);
+                    tc_fence_after();
+                    const uint32_t a_lo = a_lo0 + stage * (A_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (B_BYTES >> 4);
+                    /* 16 BF16 along K = 32 bytes = 2 descriptor address units */
+                    if (kb == 0) umma_ss<false>(d_tmem, a_lo, b_lo, idesc, leader);
+                    else umma_ss<true>(d_tmem, a_lo, b_lo, idesc, leader);
+#pragma unroll
+                    for (int k = 1; k < BK / 16; k++)
+                        umma_ss<true>(d_tmem, a_lo + 2 * k, b_lo + 2 * k, idesc, leader);
+                    umma_commit_if(empty_bar + 8 * stage, leader);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (!alive) break;
-                umma_commit(acc_full + 8 * acc);
+                umma_commit_if(acc_full + 8 * acc, leader);
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
@@ -179,7 +252,15 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t row = m_blk * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
             const bool row_ok = row < args.rows;
-            if (EPI == H3B_EPI_SWIGLU) {
+            if (EPI == H3B_EPI_QKV_ROPE) {
+                /* the tile's 256 columns are two whole 128-column units of the grouped row */
+#pragma unroll 1
+                for (uint32_t u = 0; u < 2; u++) {
+                    const uint32_t unit = n_blk * 2 + u;
+                    if (unit < args.heads * 3)
+                        qkv_unit_epilogue(args, lane_addr + u * 128, unit, row, row_ok);
+                }
+            } else if (EPI == H3B_EPI_SWIGLU) {
                 uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * 128;
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
@@ -369,7 +450,8 @@ bool env_flag(const char *name) {
 template <int EPI>
 int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t weight_rows,
-              uint32_t out_cols, uint32_t tiles_n, uint32_t up_offset) {
+              uint32_t out_cols, uint32_t tiles_n, uint32_t up_offset,
+              const TcArgs *extra = nullptr) {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(h3b_gemm_tc<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -381,7 +463,8 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
     }
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, x, rows, k, BM) || !make_map(&map_b, w, weight_rows, k, 128)) return 0;
-    TcArgs args;
+    TcArgs args = {};
+    if (extra) args = *extra;
     args.out = out;
     args.bias = bias;
     args.status = gpu->status_device;
@@ -431,6 +514,30 @@ int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t 
     }
     launch_simt<uint16_t, uint16_t>(gpu, x, w, bias, out, nullptr, rows, k, n);
     return h3b_launched(gpu, what, H3B_LINEAR);
+}
+
+int h3b_qkv_rope_gemm(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const uint16_t *x,
+                      const uint16_t *w, const uint16_t *q_norm, const uint16_t *k_norm,
+                      const uint16_t *rope_cos, const uint16_t *rope_sin, uint32_t rows,
+                      uint32_t in_dim, uint32_t heads, float eps) {
+    const uint32_t n = heads * 3 * 128;
+    bool aligned = h3b_aligned16(q) && h3b_aligned16(k) && h3b_aligned16(v) && h3b_aligned16(x) &&
+                   h3b_aligned16(w) && h3b_aligned16(q_norm) && h3b_aligned16(k_norm) &&
+                   h3b_aligned16(rope_cos) && h3b_aligned16(rope_sin);
+    if (!aligned || !rows || !heads || !in_dim || in_dim % 8 != 0 ||
+        env_flag("H3B_NO_TENSOR_CORES") || env_flag("H3B_UNFUSED_QKV_ROPE") ||
+        double(rows) * n * in_dim < 32.0 * 256 * 256)
+        return -1;
+    TcArgs extra = {};
+    extra.q_out = q; extra.k_out = k; extra.v_out = v;
+    extra.q_norm = q_norm; extra.k_norm = k_norm;
+    extra.rope_cos = rope_cos; extra.rope_sin = rope_sin;
+    extra.heads = heads;
+    extra.eps = eps;
+    if (!launch_tc<H3B_EPI_QKV_ROPE>(gpu, nullptr, x, w, nullptr, rows, in_dim, n, n,
+                                     (n + BN - 1) / BN, 0, &extra))
+        return h3b_fail(gpu, "cannot set up the fused QKV projection kernel");
+    return h3b_launched(gpu, "grouped_qkv_linear_rope_bf16", H3B_LINEAR);
 }
 
 /* ================================================================= C ABI */

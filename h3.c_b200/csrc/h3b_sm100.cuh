@@ -142,6 +142,61 @@ __host__ __device__ constexpr uint32_t instruction_desc(int m, int n) {
 }
 
 
+/* ---- descriptor words for hot issue loops -----------------------------------------
+ * The single thread that issues tcgen05.mma is a scalar instruction stream; building a
+ * 64-bit descriptor per instruction costs more than a small MMA takes. The upper word of
+ * a descriptor is constant per operand kind and the lower word is (address >> 4) plus the
+ * leading-byte-offset field, so a loop only adds a constant to the lower word. */
+constexpr uint32_t DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);   /* SBO | version | SW128 */
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem_addr) {
+    return ((smem_addr >> 4) & 0x3fffu) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t desc_lo_nmajor(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3fffu) | ((lbo_bytes >> 4) << 16);
+}
+
+/* The issuing warp runs its loop with all 32 lanes converged, so addresses and descriptor
+ * words stay warp-uniform (no per-instruction moves from the vector to the uniform register
+ * file); only the tcgen05 instruction itself is predicated on the `leader` lane.
+ * D[tmem] (+)= A[smem] . B[smem]; ACC is a compile-time flag. */
+template <bool ACC>
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t leader = 1) {
+    asm volatile(
+        "{\n\t.reg .pred p, l;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.u32 p, %5, 0;\n\t"
+        "setp.ne.u32 l, %6, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "@l tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(DESC_HI_SW128), "n"(ACC ? 1 : 0),
+          "r"(leader)
+        : "memory");
+}
+
+/* D[tmem] (+)= A[tmem] . B[smem] */
+template <bool ACC>
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t leader = 1) {
+    asm volatile(
+        "{\n\t.reg .pred p, l;\n\t.reg .b64 db;\n\t"
+        "setp.ne.u32 p, %5, 0;\n\t"
+        "setp.ne.u32 l, %6, 0;\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "@l tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(DESC_HI_SW128), "n"(ACC ? 1 : 0),
+          "r"(leader)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_if(uint32_t bar, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred l;\n\tsetp.ne.u32 l, %1, 0;\n\t"
+        "@l tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(leader)
+        : "memory");
+}
+
 /* two F32 -> packed BF16x2, round to nearest even (one cvt instruction) */
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
