@@ -1,0 +1,33 @@
+"""Sequence-parallel block on real GPUs: N ranks (one process per GPU, NCCL all-to-all around
+attention) must reproduce the single-device block. Needs at least two GPUs; skipped otherwise."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def gpu_count():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.mark.parametrize("rows", [300, 301])      # 301: the last rank holds a padding row
+def test_sharded_block_matches_oracle(rows):
+    n = gpu_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    port = 29600 + os.getpid() % 300
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                          f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                          "--master-port", str(port), str(ROOT / "tests" / "ulysses_worker.py"), str(rows)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    print(res.stdout[-2000:])
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "PASS" in res.stdout

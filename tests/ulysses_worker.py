@@ -1,0 +1,73 @@
+"""Worker for tests/test_gpu_ulysses.py: run under torch.distributed.run with N ranks.
+
+Every rank holds a row slice of one DiT block's input, runs the block through the host
+driver with the NCCL all-to-all exchange around attention, and rank 0 checks the gathered
+output against the CPU oracle's single-device block (per-block bar)."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+for p in (ROOT, ROOT / "oracle", ROOT / "tests"):
+    sys.path.insert(0, str(p))
+
+import h3_oracle as o  # noqa: E402
+from bench import NcclExchange, TorchMemory  # noqa: E402
+from block_case import make_block_case, upload_block  # noqa: E402
+from parity import block_metrics  # noqa: E402
+import __graft_entry__ as entry  # noqa: E402
+
+
+def main():
+    rows = int(sys.argv[1]) if len(sys.argv) > 1 else 301
+    pkg = entry.load_package()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    gpu = pkg.Gpu(local)
+    mem = TorchMemory(torch, pkg, gpu, device)
+    case = make_block_case(rows=rows, text_rows=37, heads=8, hidden=512, ffn=1024, seed=5)
+    shape = pkg.DitShape(hidden=512, heads=8, ffn=1024, blocks=1)
+    dit = pkg.Dit(gpu, shape, rows, exchange=NcclExchange(dist, mem, world, rank),
+                  alloc=lambda n: mem.bf16(n))
+    w = upload_block(pkg, gpu, case)
+    r0, rl, valid = dit.row_begin, dit.rows_local, dit.rows_valid
+
+    def local_slice(a, width, dtype):
+        out = np.zeros(rl * width, dtype)
+        out[:valid * width] = a.reshape(rows, width)[r0:r0 + valid].reshape(-1)
+        return out
+
+    row_map = gpu.u32(local_slice(case.row_map, 1, np.uint32))
+    cos = gpu.bf16(local_slice(case.rope_cos, 48, np.uint16))
+    sin = gpu.bf16(local_slice(case.rope_sin, 48, np.uint16))
+    dit.hidden.write(local_slice(case.hidden, 512, np.uint16))
+    gpu.begin()
+    dit.run_block(w, row_map, cos, sin, False, None)
+    gpu.submit()
+    mine = torch.from_numpy(dit.hidden.read().astype(np.int32)).to(device)
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    ok = True
+    if rank == 0:
+        full = np.concatenate([g.cpu().numpy().astype(np.uint16) for g in gathered])[:rows * 512]
+        want = o.dit_block(case.hidden, case.weights, case.row_map, case.rope_cos, case.rope_sin,
+                           rows=rows, width=512, heads=8, head_dim=128, ffn=1024, rope_half=48, round_p=1)
+        r, m = block_metrics(full, want)
+        ok = r <= 1e-2 and m <= 5e-2
+        print(f"ulysses world={world} rows={rows}: rel_l2={r:.3e} max_abs={m:.3e} {'PASS' if ok else 'FAIL'}",
+              flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    gpu.close()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
