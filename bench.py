@@ -43,6 +43,11 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel, from the
+# ncu capture summarised in profiles/h3b_gemm_tc_qkv_norm_rope_c3.md (workload, ranks) -> bytes
+NCU_DRAM_BYTES_PER_LAUNCH = {}
+
+
 def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -413,9 +418,11 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         w = step.blocks[0]
         kernels = {}
         qkv_flops = 2.0 * rows * s.hidden * 3 * s.inner
-        kernels["gemm_qkv"] = time_kernel(
-            torch, gpu, lambda: gpu.op("linear_bf16", dit.qkv, dit.mod_attention, w.qkv, None, rows,
-                                       s.hidden, 3 * s.inner), qkv_flops)
+        kernels["qkv_proj_norm_rope"] = time_kernel(
+            torch, gpu, lambda: gpu.op("grouped_qkv_linear_rope_bf16", dit.query, dit.key, dit.value,
+                                       dit.qkv, dit.mod_attention, w.qkv, w.q_norm, w.k_norm,
+                                       step.rope_cos, step.rope_sin, rows, s.hidden, s.heads,
+                                       s.head_dim, s.rope_half, s.eps), qkv_flops)
         mlp_flops = 2.0 * rows * s.hidden * 2 * s.ffn + 2.0 * rows * s.ffn * s.hidden
         kernels["mlp_fc1_swiglu_fc2"] = time_kernel(
             torch, gpu, lambda: gpu.op("mlp_bf16", dit.attention_output, dit.mod_mlp, w.fc1, w.fc2,
@@ -430,11 +437,14 @@ def run_gpu_arm(args, shape, sequence, text_rows):
                 torch, gpu, lambda: gpu.op("sdpa_bf16", dit.attention_heads, dit.query, dit.key,
                                            dit.value, sequence, s.heads, s.head_dim, s.scale),
                 attn_flops)
-        qkv_ms, qkv_tf = kernels["gemm_qkv"]
-        roofline = {"bound": "tensor", "kernel": "h3b_gemm_tc<store> (QKV projection)",
+        qkv_ms, qkv_tf = kernels["qkv_proj_norm_rope"]
+        roofline = {"bound": "tensor",
+                    "kernel": "h3b_gemm_tc<qkv+norm+rope> (QKV projection with fused head norm and RoPE)",
                     "achieved": qkv_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": qkv_tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst",
-                    "ms_per_launch": qkv_ms, "flops_per_launch": qkv_flops, "traffic": None}
+                    "ms_per_launch": qkv_ms, "flops_per_launch": qkv_flops,
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((args.workload, world)),
+                    "traffic_unit": "bytes per launch (dram read+write, one ncu capture)"}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu_ms, desc, threads, _ = cpu_sample(s, sequence)

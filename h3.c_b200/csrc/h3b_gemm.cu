@@ -41,7 +41,6 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;                 /* one 128-byte swizzle row of BF16 */
 constexpr int STAGES = 4;
-constexpr int GROUP_M = 16;
 constexpr int A_BYTES = BM * BK * 2;   /* 16 KiB */
 constexpr int B_BYTES = BN * BK * 2;   /* 32 KiB */
 constexpr int TC_THREADS = 192;
@@ -55,6 +54,7 @@ struct TcArgs {
     uint32_t out_cols;    /* stored columns (n, or hidden for SwiGLU) */
     uint32_t k_blocks;
     uint32_t tiles_m, tiles_n;
+    uint32_t group_m;     /* row-blocks walked together so their X slabs stay in L2 */
     uint32_t up_offset;   /* SwiGLU: weight row of the first up column (= hidden) */
     /* QKV + norm + RoPE epilogue */
     uint16_t *q_out, *k_out, *v_out;
@@ -167,12 +167,12 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
 
     const uint32_t total_tiles = args.tiles_m * args.tiles_n;
-    const uint32_t group_tiles = GROUP_M * args.tiles_n;
+    const uint32_t group_tiles = args.group_m * args.tiles_n;
 
     auto tile_coords = [&](uint32_t tile, uint32_t &m_blk, uint32_t &n_blk) {
         uint32_t group = tile / group_tiles, local = tile % group_tiles;
-        uint32_t first_m = group * GROUP_M;
-        uint32_t group_m = min(args.tiles_m - first_m, uint32_t(GROUP_M));
+        uint32_t first_m = group * args.group_m;
+        uint32_t group_m = min(args.tiles_m - first_m, args.group_m);
         m_blk = first_m + local % group_m;
         n_blk = local / group_m;
     };
@@ -474,6 +474,18 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
     args.tiles_m = (rows + BM - 1) / BM;
     args.tiles_n = tiles_n;
     args.up_offset = up_offset;
+    /* Tile walk: all column blocks for a group of row blocks, then the next group. The
+     * weight is streamed from HBM once per group, the group's X rows are re-used from L2,
+     * so the group is made as tall as ~40 MB of X allows (L2 is 126 MB) and the groups are
+     * balanced. Measured with 16-row-block groups: 3.3x the algorithmic DRAM reads. */
+    {
+        const double slab = double(BM) * k * 2.0;
+        uint32_t gm = uint32_t(40.0e6 / slab);
+        gm = gm < 4 ? 4 : gm;
+        gm = gm > args.tiles_m ? args.tiles_m : gm;
+        const uint32_t groups = (args.tiles_m + gm - 1) / gm;
+        args.group_m = (args.tiles_m + groups - 1) / groups;
+    }
     uint32_t tiles = args.tiles_m * args.tiles_n;
     uint32_t grid = tiles < uint32_t(gpu->sm_count) ? tiles : uint32_t(gpu->sm_count);
     h3b_gemm_tc<EPI><<<grid, TC_THREADS, TC_SMEM, gpu->stream>>>(map_a, map_b, args);
