@@ -44,8 +44,8 @@ WORKLOADS = {
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel, from the
-# ncu capture summarised in profiles/h3b_gemm_tc_qkv_norm_rope_c3.md (workload, ranks) -> bytes
-NCU_DRAM_BYTES_PER_LAUNCH = {}
+# ncu capture summarised in profiles/h3b_gemm_tc_dram_traffic_c3.md; (workload, ranks) -> bytes
+NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 841.0e6}
 
 
 def measured_peaks():
