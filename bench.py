@@ -336,7 +336,15 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         dist.init_process_group("nccl", device_id=device)
     gpu = pkg.Gpu(local_rank)          # raises if the CUDA library or the device is missing
     mem = TorchMemory(torch, pkg, gpu, device)
-    exchange = NcclExchange(dist, mem, world, rank) if world > 1 else None
+    exchange = None
+    if world > 1 and args.exchange == "push":
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+        exchange = pkg.PeerExchange(gpu, world, rank, gather)
+    elif world > 1:
+        exchange = NcclExchange(dist, mem, world, rank)
     peaks = measured_peaks()
 
     dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
@@ -418,11 +426,17 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         w = step.blocks[0]
         kernels = {}
         qkv_flops = 2.0 * rows * s.hidden * 3 * s.inner
-        kernels["qkv_proj_norm_rope"] = time_kernel(
-            torch, gpu, lambda: gpu.op("grouped_qkv_linear_rope_bf16", dit.query, dit.key, dit.value,
-                                       dit.qkv, dit.mod_attention, w.qkv, w.q_norm, w.k_norm,
-                                       step.rope_cos, step.rope_sin, rows, s.hidden, s.heads,
-                                       s.head_dim, s.rope_half, s.eps), qkv_flops)
+        if dit.push:
+            def qkv_op():
+                gpu.op("h3x_grouped_qkv_linear_rope_push", exchange.peers, dit.mod_attention, w.qkv,
+                       w.q_norm, w.k_norm, step.rope_cos, step.rope_sin, rows, s.hidden, s.heads,
+                       s.head_dim, s.rope_half, s.eps)
+        else:
+            def qkv_op():
+                gpu.op("grouped_qkv_linear_rope_bf16", dit.query, dit.key, dit.value, dit.qkv,
+                       dit.mod_attention, w.qkv, w.q_norm, w.k_norm, step.rope_cos, step.rope_sin,
+                       rows, s.hidden, s.heads, s.head_dim, s.rope_half, s.eps)
+        kernels["qkv_proj_norm_rope"] = time_kernel(torch, gpu, qkv_op, qkv_flops)
         mlp_flops = 2.0 * rows * s.hidden * 2 * s.ffn + 2.0 * rows * s.ffn * s.hidden
         kernels["mlp_fc1_swiglu_fc2"] = time_kernel(
             torch, gpu, lambda: gpu.op("mlp_bf16", dit.attention_output, dit.mod_mlp, w.fc1, w.fc2,
@@ -467,10 +481,16 @@ def run_gpu_arm(args, shape, sequence, text_rows):
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
-        if exchange is not None:
+        if isinstance(exchange, NcclExchange):
             line["all_to_all_calls_per_step"] = exchange.calls // max(1, (args.warmup + 2 * args.steps + 1))
+        if world > 1:
+            line["config"]["exchange"] = ("peer stores from the QKV and attention epilogues + 2 flag barriers per block"
+                                          if dit.push else "pack + NCCL all-to-all + unpack")
     if world > 1:
         dist.barrier()
+        if dit.push:
+            torch.cuda.synchronize()
+            exchange.close()
         dist.destroy_process_group()
     gpu.close()
     if line is not None:
@@ -486,6 +506,8 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=50)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
+                    help="N>1: peer stores fused into the kernels, or pack + NCCL all-to-all + unpack")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

@@ -43,6 +43,12 @@ class DeviceInfo(C.Structure):
                 ("compute_minor", C.c_int), ("multiprocessors", C.c_int)]
 
 
+class UlyssesPeers(C.Structure):
+    """h3x_ulysses_peers: pointers to every rank's exchange buffers as mapped in this process."""
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("rows_local", C.c_uint32)] + \
+               [(n, C.c_void_p * 8) for n in ("q", "k", "v", "o", "flags")]
+
+
 _CTYPES = {
     "void": None, "int": C.c_int, "float": C.c_float, "double": C.c_double,
     "uint32_t": C.c_uint32, "uint64_t": C.c_uint64, "size_t": C.c_size_t,
@@ -228,7 +234,8 @@ class Gpu:
     # ---- ops: gpu.op("linear_bf16", out, x, w, None, rows, k, n) calls h3_gpu_linear_bf16
     def op(self, name: str, *args) -> None:
         fn = getattr(self.lib, name if name.startswith("h3") else "h3_gpu_" + name)
-        raw = [a.handle if isinstance(a, Tensor) else a for a in args]
+        raw = [a.handle if isinstance(a, Tensor) else C.byref(a) if isinstance(a, C.Structure)
+               else a for a in args]
         if not fn(self.handle, *raw):
             raise H3Error(f"{name} failed: {self.error()}")
 

@@ -292,6 +292,10 @@ struct AttnArgs {
     uint32_t seq, heads;
     float scale_log2;
     int head_major;
+    /* sequence-parallel push (world != 0): output row r goes to rank r / rows_local, into
+     * [rows_local][heads_total][128] at head head0 + head */
+    uint32_t world, rows_local, heads_total, head0;
+    uint16_t *peer_o[8];
     long long *trace;   /* optional [role][tile][event] clock64 stamps of CTA (0,0); NULL = off */
 };
 
@@ -339,6 +343,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
  * swizzle and read as an N-major B operand: along N, 64-element groups are one box
  * (16384 bytes) apart = leading byte offset; along K, groups of 8 keys are 1024 bytes
  * apart = stride byte offset; 16 keys (one instruction) are 2048 bytes. */
+template <bool PUSH>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
@@ -617,9 +622,20 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         if (alive && mbar_wait(o_done, 0, stop)) {
             tc_fence_after();
             const float inv = 1.0f / (l_run + *theirs);
-            uint16_t *dst = (args.head_major
-                                 ? args.out + (size_t(head) * args.seq + row) * AT_D
-                                 : args.out + (size_t(row) * args.heads + head) * AT_D) + half * 64;
+            uint16_t *dst;
+            if (PUSH) {
+                const uint32_t owner = min(row / args.rows_local, args.world - 1);
+                uint16_t *base = args.peer_o[0];
+#pragma unroll
+                for (uint32_t r = 1; r < 8; r++)
+                    if (r == owner) base = args.peer_o[r];
+                dst = base +
+                      (size_t(row - owner * args.rows_local) * args.heads_total + args.head0 + head) * AT_D;
+            } else {
+                dst = args.head_major ? args.out + (size_t(head) * args.seq + row) * AT_D
+                                      : args.out + (size_t(row) * args.heads + head) * AT_D;
+            }
+            dst += half * 64;
 #pragma unroll 1
             for (int c = 0; c < 2; c++) {
                 uint32_t o[32];
@@ -671,24 +687,30 @@ bool make_qkv_map(CUtensorMap *map, const uint16_t *data, uint32_t rows, uint32_
 
 int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
                 const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t seq,
-                uint32_t heads, uint32_t hd, float scale, int head_major) {
+                uint32_t heads, uint32_t hd, float scale, int head_major,
+                const h3x_ulysses_peers *peers = nullptr, uint32_t heads_total = 0) {
     size_t count = size_t(seq) * heads * hd;
     if (!seq || !heads || !hd) return h3b_fail(gpu, "SDPA shape is empty");
     if (!h3b_need_command(gpu)) return 0;
-    if (!query || !key || !value || !output || query->dtype != H3_GPU_BF16 ||
-        key->dtype != H3_GPU_BF16 || value->dtype != H3_GPU_BF16 || output->dtype != H3_GPU_BF16)
+    if (!query || !key || !value || (!output && !peers) || query->dtype != H3_GPU_BF16 ||
+        key->dtype != H3_GPU_BF16 || value->dtype != H3_GPU_BF16 ||
+        (output && output->dtype != H3_GPU_BF16))
         return h3b_fail(gpu, "SDPA tensor dtype mismatch");
     if (query->elements < count || key->elements < count || value->elements < count ||
-        output->elements < count)
+        (output && output->elements < count))
         return h3b_fail(gpu, "SDPA tensor is too small");
     const char *force = getenv("H3B_SDPA_SIMT");
     bool simt = force && *force && strcmp(force, "0") != 0;
     bool aligned = h3b_aligned16(query->data) && h3b_aligned16(key->data) &&
-                   h3b_aligned16(value->data) && h3b_aligned16(output->data);
+                   h3b_aligned16(value->data) && (!output || h3b_aligned16(output->data));
+    if (peers && !(hd == AT_D && aligned && scale > 0.0f))
+        return h3b_fail(gpu, "the push variant of SDPA needs head_dim 128 and aligned tensors");
     if (hd == AT_D && aligned && !simt && scale > 0.0f) {
         static bool configured = false;
         if (!configured) {
-            if (cudaFuncSetAttribute(h3b_sdpa_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            if (cudaFuncSetAttribute(h3b_sdpa_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(AT_SMEM)) != cudaSuccess ||
+                cudaFuncSetAttribute(h3b_sdpa_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(AT_SMEM)) != cudaSuccess) {
                 cudaGetLastError();
                 return h3b_fail(gpu, "cannot reserve shared memory for the attention kernel");
@@ -700,8 +722,16 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
             !make_qkv_map(&map_k, h3b_ptr<uint16_t>(key), seq, heads, AT_KV) ||
             !make_qkv_map(&map_v, h3b_ptr<uint16_t>(value), seq, heads, AT_KV))
             return h3b_fail(gpu, "cannot encode the attention tensor maps");
-        AttnArgs args;
-        args.out = h3b_ptr<uint16_t>(output);
+        AttnArgs args = {};
+        args.out = output ? h3b_ptr<uint16_t>(output) : nullptr;
+        if (peers) {
+            args.world = peers->world;
+            args.rows_local = peers->rows_local;
+            args.heads_total = heads_total;
+            args.head0 = peers->rank * heads;
+            for (uint32_t r = 0; r < peers->world; r++)
+                args.peer_o[r] = static_cast<uint16_t *>(peers->o[r]);
+        }
         args.status = gpu->status_device;
         args.seq = seq;
         args.heads = heads;
@@ -710,7 +740,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         args.trace = nullptr;
         if (const char *t = getenv("H3B_ATTN_TRACE_PTR")) args.trace = reinterpret_cast<long long *>(strtoull(t, nullptr, 0));
         dim3 grid((seq + AT_Q - 1) / AT_Q, heads);
-        h3b_sdpa_tc<<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
+        if (peers) h3b_sdpa_tc<true><<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
+        else h3b_sdpa_tc<false><<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
         return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
     }
     if (hd > uint32_t(kSimtThreads * kSimtMaxDimsPerThread))
@@ -854,4 +885,58 @@ extern "C" int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *ou
                                                   uint32_t heads, uint32_t head_dim,
                                                   float scale) {
     return sdpa_common(gpu, output, query, key, value, sequence, heads, head_dim, scale, 1);
+}
+
+/* ---- sequence-parallel variants: the exchange is the kernels' own peer stores ---- */
+
+static int peers_ok(h3_gpu *gpu, const h3x_ulysses_peers *peers, uint32_t heads) {
+    if (!peers || !peers->world || peers->world > 8 || peers->rank >= peers->world ||
+        !peers->rows_local || heads % peers->world)
+        return h3b_fail(gpu, "invalid sequence-parallel peer table");
+    return 1;
+}
+
+extern "C" int h3x_grouped_qkv_linear_rope_push(
+    h3_gpu *gpu, const h3x_ulysses_peers *peers, const h3_gpu_tensor *input,
+    const h3_gpu_tensor *weight, const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+    const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin, uint32_t rows,
+    uint32_t input_dim, uint32_t heads, uint32_t head_dim, uint32_t rope_half, float epsilon) {
+    if (!gpu || !peers_ok(gpu, peers, heads)) return 0;
+    if (head_dim != 128 || rope_half != 48 || rows > peers->rows_local)
+        return h3b_fail(gpu, "the push variant needs head_dim 128, rope_half 48 and rows <= rows_local");
+    for (uint32_t r = 0; r < peers->world; r++)
+        if (!peers->q[r] || !peers->k[r] || !peers->v[r] || !h3b_aligned16(peers->q[r]) ||
+            !h3b_aligned16(peers->k[r]) || !h3b_aligned16(peers->v[r]))
+            return h3b_fail(gpu, "peer q/k/v buffers must be non-null and 16-byte aligned");
+    uint32_t inner = heads * head_dim;
+    if (!h3b_need(gpu, input, H3_GPU_BF16, size_t(rows) * input_dim, "linear input") ||
+        !h3b_need(gpu, weight, H3_GPU_BF16, size_t(inner) * 3 * input_dim, "linear weight") ||
+        !h3b_need(gpu, q_norm, H3_GPU_BF16, head_dim, "Q norm") ||
+        !h3b_need(gpu, k_norm, H3_GPU_BF16, head_dim, "K norm") ||
+        !h3b_need(gpu, rope_cos, H3_GPU_BF16, size_t(rows) * rope_half, "RoPE cosine") ||
+        !h3b_need(gpu, rope_sin, H3_GPU_BF16, size_t(rows) * rope_half, "RoPE sine") ||
+        !h3b_need_command(gpu))
+        return 0;
+    if (!rows) return 1;
+    int fused = h3b_qkv_rope_gemm(gpu, nullptr, nullptr, nullptr, h3b_ptr<uint16_t>(input),
+                                  h3b_ptr<uint16_t>(weight), h3b_ptr<uint16_t>(q_norm),
+                                  h3b_ptr<uint16_t>(k_norm), h3b_ptr<uint16_t>(rope_cos),
+                                  h3b_ptr<uint16_t>(rope_sin), rows, input_dim, heads, epsilon, peers);
+    if (fused < 0) return h3b_fail(gpu, "shape not supported by the fused QKV projection kernel");
+    if (fused == 1) gpu->stats.direct_dispatches++;
+    return fused;
+}
+
+extern "C" int h3x_sdpa_push(h3_gpu *gpu, const h3x_ulysses_peers *peers,
+                             const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                             const h3_gpu_tensor *value, uint32_t sequence, uint32_t heads_total,
+                             uint32_t head_dim, float scale) {
+    if (!gpu || !peers_ok(gpu, peers, heads_total)) return 0;
+    for (uint32_t r = 0; r < peers->world; r++)
+        if (!peers->o[r] || !h3b_aligned16(peers->o[r]))
+            return h3b_fail(gpu, "peer output buffers must be non-null and 16-byte aligned");
+    if (size_t(peers->rows_local) * peers->world < sequence)
+        return h3b_fail(gpu, "rows_local * world does not cover the sequence");
+    return sdpa_common(gpu, nullptr, query, key, value, sequence, heads_total / peers->world,
+                       head_dim, scale, 0, peers, heads_total);
 }

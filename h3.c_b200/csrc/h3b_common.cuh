@@ -30,6 +30,7 @@ enum : int {
     H3B_STATUS_OK = 0,
     H3B_STATUS_GEMM_TIMEOUT = 1,
     H3B_STATUS_ATTN_TIMEOUT = 2,
+    H3B_STATUS_PEER_TIMEOUT = 3,
 };
 
 struct h3b_pinned_slot {
@@ -169,7 +170,8 @@ enum h3b_gemm_epilogue {
 int h3b_qkv_rope_gemm(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const uint16_t *x,
                       const uint16_t *w, const uint16_t *q_norm, const uint16_t *k_norm,
                       const uint16_t *rope_cos, const uint16_t *rope_sin, uint32_t rows,
-                      uint32_t in_dim, uint32_t heads, float eps);
+                      uint32_t in_dim, uint32_t heads, float eps,
+                      const h3x_ulysses_peers *peers = nullptr);
 int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
                   const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t n,
                   h3b_gemm_epilogue epilogue, const char *what);

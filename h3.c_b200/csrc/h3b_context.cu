@@ -256,6 +256,9 @@ extern "C" int h3_gpu_submit(h3_gpu *gpu) {
     if (kernel_status != H3B_STATUS_OK) {
         cudaMemsetAsync(gpu->status_device, 0, sizeof(int), gpu->stream);
         gpu->status_seen = kernel_status;
+        if (kernel_status == H3B_STATUS_PEER_TIMEOUT)
+            return h3b_fail(gpu, "a peer barrier gave up waiting for another rank (status %d)",
+                            kernel_status);
         return h3b_fail(gpu, "a %s kernel gave up waiting on its pipeline (status %d)",
                         kernel_status == H3B_STATUS_GEMM_TIMEOUT ? "GEMM" : "attention",
                         kernel_status);

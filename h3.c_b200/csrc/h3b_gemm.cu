@@ -61,6 +61,10 @@ struct TcArgs {
     const uint16_t *q_norm, *k_norm, *rope_cos, *rope_sin;
     uint32_t heads;
     float eps;
+    /* sequence-parallel push: head h belongs to rank h / heads_per_rank, whose gathered
+     * buffers take this rank's rows at row offset rank * rows_local (world == 0: local) */
+    uint32_t world, rank, rows_local, heads_per_rank;
+    uint16_t *peer_q[8], *peer_k[8], *peer_v[8];
 };
 
 constexpr int ROPE_HALF = 48;   /* the model's RoPE width (h3_dit.c ROPE_HALF) */
@@ -72,8 +76,15 @@ constexpr int ROPE_HALF = 48;   /* the model's RoPE width (h3_dit.c ROPE_HALF) *
 __device__ __forceinline__ void qkv_unit_epilogue(const TcArgs &args, uint32_t lane_addr,
                                                   uint32_t unit, uint32_t row, bool row_ok) {
     const uint32_t head = unit / 3, kind = unit % 3;
-    uint16_t *dst = (kind == 0 ? args.q_out : kind == 1 ? args.k_out : args.v_out) +
-                    (size_t(row) * args.heads + head) * 128;
+    uint16_t *dst;
+    if (args.world) {
+        const uint32_t owner = head / args.heads_per_rank, local_head = head % args.heads_per_rank;
+        uint16_t *base = kind == 0 ? args.peer_q[owner] : kind == 1 ? args.peer_k[owner] : args.peer_v[owner];
+        dst = base + ((size_t(args.rank) * args.rows_local + row) * args.heads_per_rank + local_head) * 128;
+    } else {
+        dst = (kind == 0 ? args.q_out : kind == 1 ? args.k_out : args.v_out) +
+              (size_t(row) * args.heads + head) * 128;
+    }
     float x[128];
 #pragma unroll
     for (int c = 0; c < 4; c++) {
@@ -531,9 +542,9 @@ int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t 
 int h3b_qkv_rope_gemm(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const uint16_t *x,
                       const uint16_t *w, const uint16_t *q_norm, const uint16_t *k_norm,
                       const uint16_t *rope_cos, const uint16_t *rope_sin, uint32_t rows,
-                      uint32_t in_dim, uint32_t heads, float eps) {
+                      uint32_t in_dim, uint32_t heads, float eps, const h3x_ulysses_peers *peers) {
     const uint32_t n = heads * 3 * 128;
-    bool aligned = h3b_aligned16(q) && h3b_aligned16(k) && h3b_aligned16(v) && h3b_aligned16(x) &&
+    bool aligned = (peers || (h3b_aligned16(q) && h3b_aligned16(k) && h3b_aligned16(v))) && h3b_aligned16(x) &&
                    h3b_aligned16(w) && h3b_aligned16(q_norm) && h3b_aligned16(k_norm) &&
                    h3b_aligned16(rope_cos) && h3b_aligned16(rope_sin);
     if (!aligned || !rows || !heads || !in_dim || in_dim % 8 != 0 ||
@@ -546,6 +557,17 @@ int h3b_qkv_rope_gemm(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const 
     extra.rope_cos = rope_cos; extra.rope_sin = rope_sin;
     extra.heads = heads;
     extra.eps = eps;
+    if (peers) {
+        extra.world = peers->world;
+        extra.rank = peers->rank;
+        extra.rows_local = peers->rows_local;
+        extra.heads_per_rank = heads / peers->world;
+        for (uint32_t r = 0; r < peers->world; r++) {
+            extra.peer_q[r] = static_cast<uint16_t *>(peers->q[r]);
+            extra.peer_k[r] = static_cast<uint16_t *>(peers->k[r]);
+            extra.peer_v[r] = static_cast<uint16_t *>(peers->v[r]);
+        }
+    }
     if (!launch_tc<H3B_EPI_QKV_ROPE>(gpu, nullptr, x, w, nullptr, rows, in_dim, n, n,
                                      (n + BN - 1) / BN, 0, &extra))
         return h3b_fail(gpu, "cannot set up the fused QKV projection kernel");

@@ -52,7 +52,95 @@ int permute(h3_gpu *gpu, h3_gpu_tensor *dst, const h3_gpu_tensor *src, uint32_t 
     return h3b_launched(gpu, what);
 }
 
+/* Flag words of one rank: [0, 8) = epoch last announced by rank r, [8] = this rank's own
+ * barrier count. One warp; lane r talks to rank r. */
+__global__ void h3b_peer_barrier(uint32_t *mine, h3x_ulysses_peers peers, int *status,
+                                 long long budget) {
+    __shared__ uint32_t epoch_shared;
+    if (threadIdx.x == 0) {
+        epoch_shared = mine[8] + 1;
+        mine[8] = epoch_shared;
+    }
+    __syncthreads();
+    const uint32_t epoch = epoch_shared;
+    if (threadIdx.x < peers.world) {
+        uint32_t *theirs = static_cast<uint32_t *>(peers.flags[threadIdx.x]) + peers.rank;
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        const uint32_t *slot = mine + threadIdx.x;
+        const long long start = clock64();
+        for (;;) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
+            if (int32_t(seen - epoch) >= 0) break;
+            if (clock64() - start > budget) {
+                atomicExch(status, H3B_STATUS_PEER_TIMEOUT);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+}
+
 }  // namespace
+
+extern "C" int h3x_peer_barrier(h3_gpu *gpu, const h3x_ulysses_peers *peers) {
+    if (!gpu) return 0;
+    if (!peers || !peers->world || peers->world > 8 || peers->rank >= peers->world)
+        return h3b_fail(gpu, "invalid sequence-parallel peer table");
+    for (uint32_t r = 0; r < peers->world; r++)
+        if (!peers->flags[r]) return h3b_fail(gpu, "peer table has no barrier words");
+    if (!h3b_need_command(gpu)) return 0;
+    h3b_peer_barrier<<<1, 32, 0, gpu->stream>>>(static_cast<uint32_t *>(peers->flags[peers->rank]),
+                                                *peers, gpu->status_device, 20000000000ll);
+    return h3b_launched(gpu, "peer_barrier");
+}
+
+extern "C" void *h3x_peer_alloc(h3_gpu *gpu, size_t bytes, void *handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (!gpu || !bytes || !handle64) {
+        h3b_fail(gpu, "peer_alloc needs a size and a handle buffer");
+        return nullptr;
+    }
+    void *block = nullptr;
+    cudaError_t status = cudaMalloc(&block, bytes);
+    if (status == cudaSuccess) status = cudaMemset(block, 0, bytes);
+    if (status == cudaSuccess) status = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t handle;
+    if (status == cudaSuccess) status = cudaIpcGetMemHandle(&handle, block);
+    if (status != cudaSuccess) {
+        if (block) cudaFree(block);
+        h3b_fail_cuda(gpu, "peer_alloc", status);
+        return nullptr;
+    }
+    memcpy(handle64, &handle, sizeof(handle));
+    return block;
+}
+
+extern "C" void *h3x_peer_open(h3_gpu *gpu, const void *handle64) {
+    if (!gpu || !handle64) return nullptr;
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, handle64, sizeof(handle));
+    void *mapped = nullptr;
+    cudaError_t status = cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess);
+    if (status != cudaSuccess) {
+        h3b_fail_cuda(gpu, "peer_open", status);
+        return nullptr;
+    }
+    return mapped;
+}
+
+extern "C" int h3x_peer_close(h3_gpu *gpu, void *mapped) {
+    if (!gpu || !mapped) return 0;
+    cudaError_t status = cudaIpcCloseMemHandle(mapped);
+    return status == cudaSuccess ? 1 : h3b_fail_cuda(gpu, "peer_close", status);
+}
+
+extern "C" int h3x_peer_free(h3_gpu *gpu, void *block) {
+    if (!gpu || !block) return 0;
+    cudaError_t status = cudaFree(block);
+    return status == cudaSuccess ? 1 : h3b_fail_cuda(gpu, "peer_free", status);
+}
 
 extern "C" int h3x_ulysses_pack_heads(h3_gpu *gpu, h3_gpu_tensor *packed, const h3_gpu_tensor *src,
                                       uint32_t rows_local, uint32_t heads, uint32_t head_dim,

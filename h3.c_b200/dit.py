@@ -11,9 +11,11 @@ call into libh3b200.so with the reference's op names and argument meaning.
 Sequence parallelism (no counterpart in the reference): each rank owns a contiguous
 slice of rows; around attention the Q/K/V slices are regrouped by head and exchanged
 all-to-all so that each rank attends over the full sequence for heads/world heads
-(Ulysses), then exchanged back. The exchange itself is supplied by the caller (an object
-with all_to_all(out, inp)), e.g. torch.distributed over NCCL; this module only issues
-the layout kernels and attention.
+(Ulysses), then exchanged back. Two forms: (1) the exchange is supplied by the caller (an
+object with all_to_all(out, inp)), e.g. torch.distributed over NCCL, and this module issues
+the layout kernels and attention; (2) the exchange object is a `PeerExchange` (peer-mapped
+buffers): the QKV projection's epilogue and the attention epilogue store straight into the
+owning rank's buffers over NVLink, and only two stream barriers per block remain.
 """
 from __future__ import annotations
 
@@ -120,13 +122,21 @@ class Dit:
         new = alloc or (lambda n: gpu.new(n, BF16))
         self.hidden = new(rows * s.hidden)
         self.mod_attention = new(rows * s.hidden)
+        self.push = world > 1 and hasattr(self.exchange, "setup")
         self.qkv = new(rows * 3 * s.inner)          # also attention_heads and mod_mlp
+        self.mod_mlp = self.qkv
+        self.attention_output = new(rows * s.hidden)  # also the MLP output
+        if self.push:
+            # q/k/v land in the owning ranks' gathered buffers, attention output in the owning
+            # rank's attention_heads: no local q/k/v, no send/receive staging
+            shared = self.exchange.setup(rows, s.heads, s.head_dim)
+            self.gathered = [shared["q"], shared["k"], shared["v"]]
+            self.attention_heads = shared["o"]
+            return
         self.query = new(rows * s.inner)
         self.key = new(rows * s.inner)
         self.value = new(rows * s.inner)
-        self.attention_output = new(rows * s.hidden)  # also the MLP output
         self.attention_heads = self.qkv
-        self.mod_mlp = self.qkv
         if world > 1:
             # exchange buffers: [world][rows_local][heads/world][head_dim] x (q, k, v) and o
             n = world * rows * (s.heads // world) * s.head_dim
@@ -164,10 +174,20 @@ class Dit:
         if not adaln_ready:
             g.op("adaln_bf16", self.mod_attention, self.hidden, w.norm1, w.modulation, row_map,
                  rows, s.hidden, s.slots, 0, 1, s.eps)
-        g.op("grouped_qkv_linear_rope_bf16", self.query, self.key, self.value, self.qkv,
-             self.mod_attention, w.qkv, w.q_norm, w.k_norm, rope_cos, rope_sin, rows, s.hidden,
-             s.heads, s.head_dim, s.rope_half, s.eps)
-        self._attention()
+        if self.push:
+            ex = self.exchange
+            g.op("h3x_grouped_qkv_linear_rope_push", ex.peers, self.mod_attention, w.qkv, w.q_norm,
+                 w.k_norm, rope_cos, rope_sin, rows, s.hidden, s.heads, s.head_dim, s.rope_half,
+                 s.eps)
+            ex.barrier()      # every rank's q/k/v rows have arrived
+            g.op("h3x_sdpa_push", ex.peers, self.gathered[0], self.gathered[1], self.gathered[2],
+                 self.sequence, s.heads, s.head_dim, s.scale)
+            ex.barrier()      # every head of this rank's rows has arrived
+        else:
+            g.op("grouped_qkv_linear_rope_bf16", self.query, self.key, self.value, self.qkv,
+                 self.mod_attention, w.qkv, w.q_norm, w.k_norm, rope_cos, rope_sin, rows, s.hidden,
+                 s.heads, s.head_dim, s.rope_half, s.eps)
+            self._attention()
         g.op("linear_bf16", self.attention_output, self.attention_heads, w.out, None, rows,
              s.inner, s.hidden)
         g.op("gate_adaln_bf16", self.hidden, self.mod_mlp, self.hidden, self.attention_output,

@@ -305,6 +305,46 @@ int h3x_ulysses_unpack_heads(h3_gpu *gpu, h3_gpu_tensor *dst, const h3_gpu_tenso
                              uint32_t rows_local, uint32_t heads, uint32_t head_dim,
                              uint32_t world);
 
+/* Sequence parallelism with the exchange fused into the producing kernels (peer stores over
+ * NVLink instead of pack + all-to-all + unpack). Every rank owns symmetric buffers that all
+ * peers can address (e.g. torch symmetric memory, cudaIpc or cuMemMap; the caller supplies
+ * the pointers as seen from THIS process):
+ *   q/k/v gathered buffers  [world * rows_local][heads / world][head_dim]   (rows in global order)
+ *   attention output buffer [rows_local][heads][head_dim]
+ * h3x_grouped_qkv_linear_rope_push: the QKV projection's epilogue (head norm + RoPE) writes
+ *   each head's q/k/v row straight into the gathered buffers of the rank that owns that head.
+ * h3x_sdpa_push: attention over this rank's heads; the epilogue writes each output row
+ *   straight into the output buffer of the rank that owns that row.
+ * Only plain global stores go to peer memory; every TMA load reads local memory. The caller
+ * orders the phases across ranks (a barrier on the stream after each of the two calls). */
+typedef struct {
+    uint32_t world, rank, rows_local;
+    void *q[8], *k[8], *v[8];   /* gathered q/k/v buffer of every rank */
+    void *o[8];                 /* attention output buffer of every rank */
+    void *flags[8];             /* barrier words of every rank: 16 x uint32, zero-initialised */
+} h3x_ulysses_peers;
+int h3x_grouped_qkv_linear_rope_push(h3_gpu *gpu, const h3x_ulysses_peers *peers,
+                                     const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
+                                     const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                                     const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                     uint32_t rows, uint32_t input_dim, uint32_t heads,
+                                     uint32_t head_dim, uint32_t rope_half, float epsilon);
+int h3x_sdpa_push(h3_gpu *gpu, const h3x_ulysses_peers *peers, const h3_gpu_tensor *query,
+                  const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t sequence,
+                  uint32_t heads_total, uint32_t head_dim, float scale);
+/* Barrier across the ranks on this context's stream: one small kernel that raises this rank's
+ * epoch in every peer's flag words (release, system scope) and waits until every peer's epoch
+ * arrived in its own. Each rank must run on its own GPU. The wait is bounded (about 10 s of
+ * GPU clock); when it runs out the kernel status word becomes non-zero and submit fails. */
+int h3x_peer_barrier(h3_gpu *gpu, const h3x_ulysses_peers *peers);
+/* Device memory that other processes on the node can map (CUDA IPC). alloc returns a zeroed
+ * cudaMalloc block and fills the 64-byte handle to send to the peers; open maps a peer's block
+ * into this process (peer access is enabled on first use); close unmaps; free releases. */
+void *h3x_peer_alloc(h3_gpu *gpu, size_t bytes, void *handle64);
+void *h3x_peer_open(h3_gpu *gpu, const void *handle64);
+int h3x_peer_close(h3_gpu *gpu, void *mapped);
+int h3x_peer_free(h3_gpu *gpu, void *block);
+
 /* Final head (adaLN + projection) for callers that must not allocate device memory.
  * No counterpart in the reference: its final head always draws its scratch from a
  * grow-only cudaMalloc'd workspace.

@@ -1,5 +1,7 @@
-"""Sequence-parallel block on real GPUs: N ranks (one process per GPU, NCCL all-to-all around
-attention) must reproduce the single-device block. Needs at least two GPUs; skipped otherwise."""
+"""Sequence-parallel block on real GPUs: N ranks (one process per GPU) must reproduce the
+single-device block, with both forms of the exchange around attention: pack + NCCL all-to-all +
+unpack, and peer stores from the kernels' epilogues over CUDA IPC mappings. Needs at least two
+GPUs; skipped otherwise."""
 import os
 import subprocess
 import sys
@@ -16,8 +18,9 @@ def gpu_count():
     return torch.cuda.device_count()
 
 
+@pytest.mark.parametrize("mode", ["nccl", "push"])
 @pytest.mark.parametrize("rows", [300, 301])      # 301: the last rank holds a padding row
-def test_sharded_block_matches_oracle(rows):
+def test_sharded_block_matches_oracle(rows, mode):
     n = gpu_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
@@ -26,7 +29,7 @@ def test_sharded_block_matches_oracle(rows):
     port = 29600 + os.getpid() % 300
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                           f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                          "--master-port", str(port), str(ROOT / "tests" / "ulysses_worker.py"), str(rows)],
+                          "--master-port", str(port), str(ROOT / "tests" / "ulysses_worker.py"), str(rows), mode],
                          capture_output=True, text=True, timeout=600, env=env)
     print(res.stdout[-2000:])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]

@@ -1,7 +1,8 @@
 """Worker for tests/test_gpu_ulysses.py: run under torch.distributed.run with N ranks.
 
 Every rank holds a row slice of one DiT block's input, runs the block through the host
-driver with the NCCL all-to-all exchange around attention, and rank 0 checks the gathered
+driver with the exchange around attention (argv[2]: nccl = pack + all-to-all + unpack,
+push = peer stores from the kernels' epilogues), and rank 0 checks the gathered
 output against the CPU oracle's single-device block (per-block bar)."""
 import os
 import sys
@@ -24,6 +25,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 def main():
     rows = int(sys.argv[1]) if len(sys.argv) > 1 else 301
+    mode = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     pkg = entry.load_package()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -34,8 +36,15 @@ def main():
     mem = TorchMemory(torch, pkg, gpu, device)
     case = make_block_case(rows=rows, text_rows=37, heads=8, hidden=512, ffn=1024, seed=5)
     shape = pkg.DitShape(hidden=512, heads=8, ffn=1024, blocks=1)
-    dit = pkg.Dit(gpu, shape, rows, exchange=NcclExchange(dist, mem, world, rank),
-                  alloc=lambda n: mem.bf16(n))
+    if mode == "push":
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+        exchange = pkg.PeerExchange(gpu, world, rank, gather)
+    else:
+        exchange = NcclExchange(dist, mem, world, rank)
+    dit = pkg.Dit(gpu, shape, rows, exchange=exchange, alloc=lambda n: mem.bf16(n))
     w = upload_block(pkg, gpu, case)
     r0, rl, valid = dit.row_begin, dit.rows_local, dit.rows_valid
 
@@ -48,6 +57,7 @@ def main():
     cos = gpu.bf16(local_slice(case.rope_cos, 48, np.uint16))
     sin = gpu.bf16(local_slice(case.rope_sin, 48, np.uint16))
     dit.hidden.write(local_slice(case.hidden, 512, np.uint16))
+    dist.barrier()
     gpu.begin()
     dit.run_block(w, row_map, cos, sin, False, None)
     gpu.submit()
@@ -61,9 +71,11 @@ def main():
                            rows=rows, width=512, heads=8, head_dim=128, ffn=1024, rope_half=48, round_p=1)
         r, m = block_metrics(full, want)
         ok = r <= 1e-2 and m <= 5e-2
-        print(f"ulysses world={world} rows={rows}: rel_l2={r:.3e} max_abs={m:.3e} {'PASS' if ok else 'FAIL'}",
+        print(f"ulysses {mode} world={world} rows={rows}: rel_l2={r:.3e} max_abs={m:.3e} {'PASS' if ok else 'FAIL'}",
               flush=True)
     dist.barrier()
+    if mode == "push":
+        exchange.close()
     dist.destroy_process_group()
     gpu.close()
     sys.exit(0 if ok else 1)
