@@ -445,6 +445,12 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         kernels["gemm_out_proj"] = time_kernel(
             torch, gpu, lambda: gpu.op("linear_bf16", dit.attention_output, dit.attention_heads, w.out,
                                        None, rows, s.inner, s.hidden), out_flops)
+        if dit.push:
+            attn_flops = 4.0 * sequence * sequence * (s.heads // world) * s.head_dim
+            kernels["attention"] = time_kernel(
+                torch, gpu, lambda: gpu.op("h3x_sdpa_push", exchange.peers, dit.gathered[0],
+                                           dit.gathered[1], dit.gathered[2], sequence, s.heads,
+                                           s.head_dim, s.scale), attn_flops)
         if world == 1:
             attn_flops = 4.0 * sequence * sequence * s.heads * s.head_dim
             kernels["attention"] = time_kernel(

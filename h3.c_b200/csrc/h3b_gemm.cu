@@ -45,6 +45,10 @@ constexpr int A_BYTES = BM * BK * 2;   /* 16 KiB */
 constexpr int B_BYTES = BN * BK * 2;   /* 32 KiB */
 constexpr int TC_THREADS = 192;
 constexpr size_t TC_SMEM = size_t(STAGES) * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+/* the QKV epilogue turns its row-per-thread results into whole-row stores through an
+ * 8 KiB staging area per epilogue warp */
+constexpr int QKV_STAGE_BYTES = 32 * 256;
+constexpr size_t TC_SMEM_QKV = TC_SMEM + 4 * QKV_STAGE_BYTES;
 
 struct TcArgs {
     uint16_t *out;
@@ -74,16 +78,20 @@ constexpr int ROPE_HALF = 48;   /* the model's RoPE width (h3_dit.c ROPE_HALF) *
  * RMSNorm over the 128 values with the head-norm weight, half-pair RoPE on dims [0,96),
  * BF16 store. Same expression order as the stand-alone kernel. */
 __device__ __forceinline__ void qkv_unit_epilogue(const TcArgs &args, uint32_t lane_addr,
-                                                  uint32_t unit, uint32_t row, bool row_ok) {
+                                                  uint32_t unit, uint32_t row, bool row_ok,
+                                                  uint32_t stage_smem, uint32_t lane) {
     const uint32_t head = unit / 3, kind = unit % 3;
-    uint16_t *dst;
+    /* dst0 = where row 0 of this rank's slice goes for this head; rows are row_stride apart */
+    uint16_t *dst0;
+    uint32_t row_stride;
     if (args.world) {
         const uint32_t owner = head / args.heads_per_rank, local_head = head % args.heads_per_rank;
         uint16_t *base = kind == 0 ? args.peer_q[owner] : kind == 1 ? args.peer_k[owner] : args.peer_v[owner];
-        dst = base + ((size_t(args.rank) * args.rows_local + row) * args.heads_per_rank + local_head) * 128;
+        row_stride = args.heads_per_rank * 128;
+        dst0 = base + (size_t(args.rank) * args.rows_local * args.heads_per_rank + local_head) * 128;
     } else {
-        dst = (kind == 0 ? args.q_out : kind == 1 ? args.k_out : args.v_out) +
-              (size_t(row) * args.heads + head) * 128;
+        row_stride = args.heads * 128;
+        dst0 = (kind == 0 ? args.q_out : kind == 1 ? args.k_out : args.v_out) + size_t(head) * 128;
     }
     float x[128];
 #pragma unroll
@@ -128,13 +136,31 @@ __device__ __forceinline__ void qkv_unit_epilogue(const TcArgs &args, uint32_t l
             }
         }
     }
-    if (row_ok) {
+    /* Each thread holds one 256-byte row. Through the warp's staging area (16-byte chunks,
+     * chunk index XOR row so that neither side has bank conflicts) the warp writes two whole
+     * rows per store instruction: full 128-byte lines, which matters when the destination is
+     * another GPU's memory. */
 #pragma unroll
-        for (int v = 0; v < 16; v++)
-            *reinterpret_cast<uint4 *>(dst + v * 8) =
-                make_uint4(pack_bf16(x[8 * v], x[8 * v + 1]), pack_bf16(x[8 * v + 2], x[8 * v + 3]),
-                           pack_bf16(x[8 * v + 4], x[8 * v + 5]), pack_bf16(x[8 * v + 6], x[8 * v + 7]));
+    for (uint32_t v = 0; v < 16; v++) {
+        const uint32_t addr = stage_smem + lane * 256 + ((v ^ (lane & 15)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                     "r"(pack_bf16(x[8 * v], x[8 * v + 1])), "r"(pack_bf16(x[8 * v + 2], x[8 * v + 3])),
+                     "r"(pack_bf16(x[8 * v + 4], x[8 * v + 5])), "r"(pack_bf16(x[8 * v + 6], x[8 * v + 7]))
+                     : "memory");
     }
+    __syncwarp();
+    const uint32_t row0 = row - lane, chunk = lane & 15;
+#pragma unroll
+    for (uint32_t j = 0; j < 16; j++) {
+        const uint32_t r = 2 * j + (lane >> 4);
+        uint4 val;
+        const uint32_t addr = stage_smem + r * 256 + ((chunk ^ (r & 15)) << 4);
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr) : "memory");
+        if (row0 + r < args.rows)
+            *reinterpret_cast<uint4 *>(dst0 + size_t(row0 + r) * row_stride + chunk * 8) = val;
+    }
+    __syncwarp();
 }
 
 template <int EPI>
@@ -269,7 +295,8 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (uint32_t u = 0; u < 2; u++) {
                     const uint32_t unit = n_blk * 2 + u;
                     if (unit < args.heads * 3)
-                        qkv_unit_epilogue(args, lane_addr + u * 128, unit, row, row_ok);
+                        qkv_unit_epilogue(args, lane_addr + u * 128, unit, row, row_ok,
+                                          bars + 256 + quarter * QKV_STAGE_BYTES, lane);
                 }
             } else if (EPI == H3B_EPI_SWIGLU) {
                 uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * 128;
@@ -464,9 +491,10 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               uint32_t out_cols, uint32_t tiles_n, uint32_t up_offset,
               const TcArgs *extra = nullptr) {
     static bool configured = false;
+    constexpr size_t smem_bytes = EPI == H3B_EPI_QKV_ROPE ? TC_SMEM_QKV : TC_SMEM;
     if (!configured) {
         if (cudaFuncSetAttribute(h3b_gemm_tc<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(TC_SMEM)) != cudaSuccess) {
+                                 int(smem_bytes)) != cudaSuccess) {
             cudaGetLastError();
             return 0;
         }
@@ -499,7 +527,7 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
     }
     uint32_t tiles = args.tiles_m * args.tiles_n;
     uint32_t grid = tiles < uint32_t(gpu->sm_count) ? tiles : uint32_t(gpu->sm_count);
-    h3b_gemm_tc<EPI><<<grid, TC_THREADS, TC_SMEM, gpu->stream>>>(map_a, map_b, args);
+    h3b_gemm_tc<EPI><<<grid, TC_THREADS, smem_bytes, gpu->stream>>>(map_a, map_b, args);
     return 1;
 }
 
