@@ -40,6 +40,10 @@ WORKLOADS = {
     "c4": (256, 50220, "864x480x121f: 50,220 video + 256 text rows (S=50,476), 50 blocks"),
     "ref512": (256, 1792 + 74, "reference-true 512x512x22f layout: 1,866 video/audio + 256 text rows"),
     "ref864": (256, 14985 + 414, "reference-true 864x480x124f layout: 15,399 video/audio + 256 text rows"),
+    "c5": (256, 50220, "864x480x121f (S=50,476), 20 Euler steps with classifier-free guidance, "
+                       "cond/uncond on two GPU groups, 50 blocks"),
+    "c5small": (256, 6144, "512x512x22f (S=6,400), 20 Euler steps with classifier-free guidance, "
+                           "cond/uncond on two GPU groups, 50 blocks"),
 }
 
 
@@ -217,6 +221,18 @@ class TorchMemory:
         return wrapped
 
     def torch_of(self, tensor):
+        """torch view of a library tensor: the torch allocation it wraps, else a zero-copy byte
+        view of the library's own allocation through the CUDA array interface (bytes, because
+        the collectives this is used for do not take 16-bit integers)."""
+        if tensor.handle not in self.by_handle:
+            size = {self.pkg.BF16: 2, self.pkg.F32: 4}[tensor.dtype]
+
+            class _Span:
+                __cuda_array_interface__ = {
+                    "shape": (tensor.elements * size,), "version": 2, "typestr": "|u1",
+                    "data": (tensor.pointer(), False)}
+            view = self.torch.as_tensor(_Span(), device=self.device)
+            self.by_handle[tensor.handle] = view
         return self.by_handle[tensor.handle]
 
 
@@ -232,7 +248,23 @@ class NcclExchange:
         self.calls += 1
 
 
-def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed=0):
+class NcclPair:
+    """Velocity swap between the two classifier-free-guidance groups: rank i of the cond group
+    and rank i of the uncond group exchange their local velocity rows over NCCL."""
+
+    def __init__(self, dist, memory, partner, is_cond):
+        self.dist, self.memory, self.partner, self.is_cond = dist, memory, partner, is_cond
+
+    def swap(self, out, inp):
+        d = self.dist
+        ops = [d.P2POp(d.isend, self.memory.torch_of(inp), self.partner),
+               d.P2POp(d.irecv, self.memory.torch_of(out), self.partner)]
+        for req in d.batch_isend_irecv(ops):
+            req.wait()
+
+
+def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed=0, time_rows=2,
+                text_seed=None):
     """Random-init weights of the architecture, modulation tables computed by the adaLN
     projection (rows = time rows, 2688 -> 3*6*5376, the load-time GEMM of the reference's
     h3_dit_schedule_precompute), rope tables and row maps for this rank's rows."""
@@ -240,7 +272,6 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     gen = torch.Generator(device=mem.device)
     gen.manual_seed(seed)
     dit = pkg.Dit(gpu, s, sequence, exchange=exchange, alloc=lambda n: mem.bf16(n))
-    time_rows = 2
     silu_time = mem.bf16(time_rows * s.time_dim, std=0.125, generator=gen)   # modulation std ~0.13
     mod_cols = s.modalities * s.slots * s.hidden
     proj_w = mem.bf16(mod_cols * s.time_dim)
@@ -267,7 +298,11 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     final_norm = mem.bf16(s.hidden, fill=1.0)
     patch_w = mem.f32(s.hidden * s.video_patch, std=0.02, generator=gen)
     patch_b = mem.f32(s.hidden, std=0.02, generator=gen)
-    text_hidden = mem.bf16(max(1, text_rows) * s.hidden, std=1.0, generator=gen)
+    text_gen = gen
+    if text_seed is not None:
+        text_gen = torch.Generator(device=mem.device)
+        text_gen.manual_seed(text_seed)
+    text_hidden = mem.bf16(max(1, text_rows) * s.hidden, std=1.0, generator=text_gen)
 
     # this rank's slice of the global rows: text rows first, then video rows
     r0, rows = dit.row_begin, dit.rows_local
@@ -290,15 +325,19 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     mem.torch_of(rope_sin).copy_(sin.reshape(-1).to(torch.bfloat16))
     tags = np.zeros(dit.rows_local * world, np.uint32)
     tags[:text_rows] = 1
-    row_map = gpu.u32(tags[r0:r0 + rows] + 3 * 1)
     local_text = max(0, min(text_rows, r0 + dit.rows_valid) - r0)
     local_video = dit.rows_valid - local_text
-    final_row_map = gpu.u32(np.ones(max(1, local_video), np.uint32))
+    # one row map per time row (row_map[row] = time_row * 3 + modality tag); the single-step
+    # bench uses time row 1
+    row_maps = [gpu.u32(tags[r0:r0 + rows] + 3 * t) for t in range(time_rows)]
+    final_row_maps = [gpu.u32(np.full(max(1, local_video), t, np.uint32)) for t in range(time_rows)]
+    row_map, final_row_map = row_maps[1], final_row_maps[1]
     step = pkg.DenoiseStep(dit, blocks, video_rows=local_video, text_rows=local_text,
                            patch_weight=patch_w, patch_bias=patch_b, text_hidden=text_hidden,
                            final_norm=final_norm, final_modulation=final_mod, final_weight=final_w,
                            final_bias=final_b, row_map=row_map, final_row_map=final_row_map,
                            rope_cos=rope_cos, rope_sin=rope_sin)
+    step.row_maps, step.final_row_maps = row_maps, final_row_maps
     return dit, step
 
 
@@ -503,6 +542,127 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         print(json.dumps(line), flush=True)
 
 
+def run_cfg_arm(args, shape, sequence, text_rows):
+    """20 Euler steps with classifier-free guidance. With N >= 2 ranks the first half evaluates
+    the cond branch and the second half the uncond branch (sequence-parallel inside each half),
+    matching ranks swap velocities over NCCL after every forward; with one rank both branches
+    run one after the other. value = seconds for the whole loop, device-timed, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus or (world > 1 and world % 2):
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node N (N = 1 or even) for --gpus N")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    gpu = pkg.Gpu(local_rank)
+    mem = TorchMemory(torch, pkg, gpu, device)
+    euler_steps, guidance = args.euler_steps, args.guidance
+    exchange, pair, group_id, half = None, None, 0, 1
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        half = world // 2
+        group_id, group_rank = rank // half, rank % half
+        groups = [dist.new_group(list(range(g * half, (g + 1) * half))) for g in range(2)]
+        if half > 1:
+            def gather(obj):
+                out = [None] * half
+                dist.all_gather_object(out, obj, group=groups[group_id])
+                return out
+            exchange = pkg.PeerExchange(gpu, half, group_rank, gather)
+        pair = NcclPair(dist, mem, (rank + half) % world, is_cond=group_id == 0)
+    dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange,
+                            time_rows=euler_steps, text_seed=2 if group_id == 0 else 4)
+    s = shape
+    n_latent = max(1, step.video_rows) * s.video_patch
+    noise = torch.Generator()
+    noise.manual_seed(1)
+    host_latent = torch.randn(n_latent, dtype=torch.float32, generator=noise).pin_memory()
+    host_final = torch.empty(n_latent, dtype=torch.float32).pin_memory()
+    latent_t = torch.empty(n_latent, dtype=torch.float32, device=device)
+    step.latent = gpu.wrap(latent_t.data_ptr(), n_latent, pkg.F32)
+    uncond = None
+    if world == 1:
+        g4 = torch.Generator(device=device)
+        g4.manual_seed(4)
+        uncond = mem.bf16(max(1, text_rows) * s.hidden, std=1.0, generator=g4)
+    sigmas = pkg.serving_sigmas(euler_steps)
+
+    def sampler_for(first, count):
+        return pkg.EulerSampler(step, sigmas[first:first + count + 1], step.row_maps[first:first + count],
+                                step.final_row_maps[first:first + count], guidance=guidance,
+                                uncond_text=uncond, pair=pair)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    latent_t.copy_(host_latent)
+    sampler_for(0, max(3, args.warmup)).run()               # untimed warm-up steps
+    full = sampler_for(0, euler_steps)
+    clock = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        clock.start()
+    before = gpu.stats()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        latent_t.copy_(host_latent, non_blocking=True)      # seeded N(0,1) noise from pinned memory
+        full.run()
+        host_final.copy_(latent_t, non_blocking=True)       # final latent back to the host
+    t1.record()
+    barrier()
+    after = gpu.stats()
+    clocks = clock.stop() if rank == 0 else None
+    seconds = t0.elapsed_time(t1) / 1e3 / args.steps
+    launches = ((after.direct_dispatches + after.mps_linear_dispatches + after.mps_sdpa_dispatches) -
+                (before.direct_dispatches + before.mps_linear_dispatches + before.mps_sdpa_dispatches))
+    if world > 1:
+        t = torch.tensor([seconds], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        seconds = float(t[0])
+        l = torch.tensor([launches], device=device, dtype=torch.int64)
+        dist.all_reduce(l)
+        launches = int(l[0])
+    if rank == 0:
+        peaks = measured_peaks()
+        forwards = 2 * euler_steps
+        flops = forwards * s.blocks * s.block_flops(sequence)
+        per_gpu = flops / seconds / 1e12 / world
+        finite = bool(torch.isfinite(host_final).all())
+        line = {
+            "metric": "cfg_denoise_total_s", "value": seconds, "unit": "s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": seconds * 1e3 / euler_steps,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": dict(workload_config(args, sequence), euler_steps=euler_steps, guidance=guidance,
+                           parallelism=(f"2 guidance groups x sp{half}" if world > 1
+                                        else "single GPU, cond and uncond in turn"),
+                           forwards_per_denoise=forwards),
+            "tflops_per_gpu": per_gpu,
+            "frac_of_bf16_peak": {"burst": per_gpu / peaks["bf16_tflops"],
+                                  "sustained": per_gpu / peaks["bf16_tflops_sustained"],
+                                  "source": peaks["source"]},
+            "e2e": {"value": seconds, "unit": "s", "h2d_bytes_per_step": n_latent * 4 * world,
+                    "d2h_bytes_per_step": n_latent * 4 * world},
+            "gpu_launches": launches, "final_latent_finite": finite, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        if exchange is not None:
+            exchange.close()
+        dist.destroy_process_group()
+    gpu.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -514,6 +674,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
                     help="N>1: peer stores fused into the kernels, or pack + NCCL all-to-all + unpack")
+    ap.add_argument("--euler-steps", type=int, default=20, help="c5: Euler steps per denoise")
+    ap.add_argument("--guidance", type=float, default=5.0,
+                    help="c5: guidance scale (the reference has no guidance pass; harness parameter)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -524,6 +687,8 @@ def main():
     sequence = text_rows + video_rows
     if args.impl == "reference":
         run_reference_arm(args, shape, sequence)
+    elif args.workload.startswith("c5"):
+        run_cfg_arm(args, shape, sequence, text_rows)
     else:
         run_gpu_arm(args, shape, sequence, text_rows)
 

@@ -337,6 +337,26 @@ __global__ void h3b_elementwise_bf16(const uint16_t *a, const uint16_t *b, uint1
     }
 }
 
+/* classifier-free guidance: out = bf16(uncond + guidance * (cond - uncond)), one fused
+ * multiply-add on the F32 difference */
+__global__ void h3b_cfg_combine_kernel(const uint16_t *cond, const uint16_t *uncond, uint16_t *out,
+                                       size_t count, float guidance, int vec) {
+    size_t i = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+    if (i >= count) return;
+    if (vec && i + 8 <= count) {
+        Vec8 c = load8(cond + i), u = load8(uncond + i), r;
+#pragma unroll
+        for (int e = 0; e < 8; e++) r.v[e] = fmaf(guidance, c.v[e] - u.v[e], u.v[e]);
+        store8(out + i, r);
+    } else {
+        size_t end = i + 8 < count ? i + 8 : count;
+        for (; i < end; i++) {
+            float u = h3b_widen(uncond[i]);
+            out[i] = h3b_narrow(fmaf(guidance, h3b_widen(cond[i]) - u, u));
+        }
+    }
+}
+
 __global__ void h3b_silu_f32_kernel(const float *in, float *out, size_t count) {
     size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < count) out[i] = silu(in[i]);
@@ -796,6 +816,23 @@ static int elementwise(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *
             elements, vec);
     }
     return h3b_launched(gpu, what);
+}
+
+extern "C" int h3x_cfg_combine_bf16(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_tensor *cond,
+                                    const h3_gpu_tensor *uncond, uint32_t elements,
+                                    float guidance) {
+    if (!gpu) return 0;
+    if (!h3b_need(gpu, cond, H3_GPU_BF16, elements, "cfg_combine cond") ||
+        !h3b_need(gpu, uncond, H3_GPU_BF16, elements, "cfg_combine uncond") ||
+        !h3b_need(gpu, out, H3_GPU_BF16, elements, "cfg_combine output") || !h3b_need_command(gpu))
+        return 0;
+    if (elements) {
+        int vec = all_aligned16({cond->data, uncond->data, out->data});
+        h3b_cfg_combine_kernel<<<blocks_for((size_t(elements) + 7) / 8, 256), 256, 0, gpu->stream>>>(
+            h3b_ptr<uint16_t>(cond), h3b_ptr<uint16_t>(uncond), h3b_ptr<uint16_t>(out), elements,
+            guidance, vec);
+    }
+    return h3b_launched(gpu, "cfg_combine_bf16");
 }
 
 extern "C" int h3_gpu_add_bf16(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_tensor *l,

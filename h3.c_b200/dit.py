@@ -123,7 +123,7 @@ class Dit:
         self.hidden = new(rows * s.hidden)
         self.mod_attention = new(rows * s.hidden)
         self.push = world > 1 and hasattr(self.exchange, "setup")
-        self.qkv = new(rows * 3 * s.inner)          # also attention_heads and mod_mlp
+        self.qkv = new(rows * max(3 * s.inner, s.hidden))   # also attention_heads and mod_mlp
         self.mod_mlp = self.qkv
         self.attention_output = new(rows * s.hidden)  # also the MLP output
         if self.push:
@@ -254,6 +254,72 @@ class DenoiseStep:
         if self.video_rows:
             self.dit.gpu.op("euler_bf16", self.latent, 0, self.velocity, self.velocity,
                             self.video_rows * self.dit.s.video_patch, delta, 0.0)
+
+
+def serving_sigmas(evaluations: int, shift: float = 12.0) -> np.ndarray:
+    """sigma[0..evaluations] of h3_serving_schedule_build (h3_host.c:152-167) for the video
+    stream (shift 12, h3_host.h:12), in F32 arithmetic like the reference."""
+    f = np.float32
+    out = np.zeros(evaluations + 1, np.float32)
+    for i in range(evaluations):
+        base = f(1.0) - f(i) / f(evaluations)
+        out[i] = f(shift) * base / (f(1.0) + (f(shift) - f(1.0)) * base)
+    return out
+
+
+class EulerSampler:
+    """The device-resident Euler loop of denoise_euler_gpu (h3_dit.c:2805-2893) with every
+    step evaluated: per step the forward with that step's time row, then
+    sample += (sigma[i] - sigma[i+1]) * velocity; one submit at the end, flush hints between.
+
+    Classifier-free guidance (no counterpart in the reference) replaces the velocity by
+    uncond + guidance * (cond - uncond) before the update, in one of two ways:
+      * `uncond_text`: this rank (group) evaluates both branches one after the other;
+      * `pair`: this rank evaluates one branch (pair.is_cond says which) and swaps velocities
+        with the matching rank of the other group through pair.swap(out, inp)."""
+
+    def __init__(self, step: DenoiseStep, sigmas: np.ndarray, row_maps: list[Tensor],
+                 final_row_maps: list[Tensor], *, guidance: float | None = None,
+                 uncond_text: Tensor | None = None, pair=None):
+        self.step, self.sigmas = step, np.asarray(sigmas, np.float32)
+        self.row_maps, self.final_row_maps = row_maps, final_row_maps
+        self.guidance, self.uncond_text, self.pair = guidance, uncond_text, pair
+        if guidance is not None and (uncond_text is None) == (pair is None):
+            raise ValueError("guidance needs exactly one of uncond_text and pair")
+        self.other = None
+        if guidance is not None:
+            self.other = step.dit.gpu.new(max(1, step.video_rows) * step.dit.s.video_patch, BF16)
+
+    def _velocity(self, index: int) -> None:
+        st, g = self.step, self.step.dit.gpu
+        st.row_map, st.final_row_map = self.row_maps[index], self.final_row_maps[index]
+        st.forward()
+        if self.guidance is None:
+            return
+        n = st.video_rows * st.dit.s.video_patch
+        if self.pair is not None:
+            self.pair.swap(self.other, st.velocity)
+            cond, uncond = (st.velocity, self.other) if self.pair.is_cond else (self.other, st.velocity)
+        else:
+            if n:
+                g.op("copy_bf16", self.other, 0, st.velocity, 0, n)
+            text, st.text_hidden = st.text_hidden, self.uncond_text
+            st.forward()
+            st.text_hidden = text
+            cond, uncond = self.other, st.velocity
+        if n:
+            g.op("h3x_cfg_combine_bf16", st.velocity, cond, uncond, n, float(self.guidance))
+
+    def run(self) -> None:
+        g = self.step.dit.gpu
+        steps = len(self.sigmas) - 1
+        g.begin()
+        for i in range(steps):
+            self._velocity(i)
+            self.step.euler(float(self.sigmas[i] - self.sigmas[i + 1]))
+            if i + 1 < steps:
+                g.flush()
+        g.submit()
 
 
 # ------------------------------------------------------------------ synthetic inputs

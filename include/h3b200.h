@@ -345,6 +345,12 @@ void *h3x_peer_open(h3_gpu *gpu, const void *handle64);
 int h3x_peer_close(h3_gpu *gpu, void *mapped);
 int h3x_peer_free(h3_gpu *gpu, void *block);
 
+/* Classifier-free guidance combine (the reference has no guidance pass; formula fixed here):
+ * out[i] = bf16(uncond[i] + guidance * (cond[i] - uncond[i])), evaluated as one F32 fused
+ * multiply-add of the F32 difference. out may alias either input. */
+int h3x_cfg_combine_bf16(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_tensor *cond,
+                         const h3_gpu_tensor *uncond, uint32_t elements, float guidance);
+
 /* Final head (adaLN + projection) for callers that must not allocate device memory.
  * No counterpart in the reference: its final head always draws its scratch from a
  * grow-only cudaMalloc'd workspace.

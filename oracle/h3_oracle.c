@@ -569,6 +569,14 @@ void h3o_euler_bf16(float *sample, const uint16_t *last,
     }
 }
 
+void h3o_cfg_combine_bf16(uint16_t *out, const uint16_t *cond, const uint16_t *uncond,
+                          size_t count, float guidance) {
+    for (size_t i = 0; i < count; i++) {
+        float u = h3o_bf16_to_f32(uncond[i]);
+        out[i] = h3o_f32_to_bf16(fmaf(guidance, h3o_bf16_to_f32(cond[i]) - u, u));
+    }
+}
+
 void h3o_token_pool_bf16(uint16_t *out, const uint16_t *in, uint16_t *original,
                          uint16_t *baseline, const uint32_t *baseline_indices,
                          const uint32_t *pairs, uint32_t rows, uint32_t width) {

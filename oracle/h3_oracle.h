@@ -148,6 +148,10 @@ void h3o_euler_bf16(float *sample, const uint16_t *last,
                     const uint16_t *previous, size_t count, float delta,
                     float ratio);
 /* h3_cuda_dit.cu:336-365 / 437-467 (token reduction pool / expand) */
+/* classifier-free guidance combine of the B200 library's h3x_cfg_combine_bf16 (no reference
+ * counterpart): out = bf16(fmaf(guidance, cond - uncond, uncond)) */
+void h3o_cfg_combine_bf16(uint16_t *out, const uint16_t *cond, const uint16_t *uncond,
+                          size_t count, float guidance);
 void h3o_token_pool_bf16(uint16_t *out, const uint16_t *in, uint16_t *original,
                          uint16_t *baseline, const uint32_t *baseline_indices,
                          const uint32_t *pairs, uint32_t rows, uint32_t width);

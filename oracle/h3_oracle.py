@@ -222,6 +222,12 @@ def euler_bf16(sample, last, previous, delta, ratio):
     return out
 
 
+def cfg_combine_bf16(cond, uncond, guidance):
+    out = np.empty_like(cond)
+    lib().h3o_cfg_combine_bf16(_p(out), _p(cond), _p(uncond), C.c_size_t(cond.size), f32(guidance))
+    return out
+
+
 def token_pool_bf16(x, baseline, baseline_indices, pairs, input_rows, rows, width):
     out = np.empty(rows * width, np.uint16)
     original = np.zeros(input_rows * width, np.uint16)

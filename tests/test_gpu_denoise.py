@@ -1,0 +1,63 @@
+"""Multi-step parity: the Euler loop (patch projection, blocks, final head, update) over several
+steps, with and without classifier-free guidance. Bar: final-latent cosine similarity >= 0.999
+(stated for the whole denoise); the small cases also hold the per-block-style rel-L2 bound.
+
+  * against the CPU oracle on a small DiT (2 blocks, 4 steps);
+  * at the model's full width against the reference's own CUDA backend (oracle/_ref/libh3ref.so)
+    driven through the same host driver with the same inputs."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from denoise_case import cosine, gpu_denoise, make_denoise_case, oracle_denoise
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+REF_CUDA = ROOT / "oracle" / "_ref" / "libh3ref.so"
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import __graft_entry__ as entry
+    return entry.load_package()
+
+
+def rel_l2(a, b):
+    a, b = a.astype(np.float64), b.astype(np.float64)
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+@pytest.mark.parametrize("guidance", [None, 3.0])
+def test_small_denoise_matches_oracle(pkg, guidance):
+    case = make_denoise_case(rows=200, text_rows=40, blocks=2, steps=4, seed=3,
+                             sigmas=pkg.serving_sigmas(4))
+    want = oracle_denoise(case, guidance)
+    gpu = pkg.Gpu(0)
+    try:
+        got, _ = gpu_denoise(pkg, gpu, case, guidance=guidance)
+    finally:
+        gpu.close()
+    cos, r = cosine(got, want), rel_l2(got, want)
+    print(f"4-step denoise guidance={guidance}: cosine={cos:.7f} rel_l2={r:.3e}")
+    # guidance multiplies the branch difference, and with it the rounding noise, by its scale
+    assert cos >= 0.999 and r <= (1e-2 if guidance is None else 3e-2)
+    assert rel_l2(want, case.latent) > 0.05      # the loop moved the latent: the check is not vacuous
+
+
+@pytest.mark.skipif(not REF_CUDA.exists(), reason="reference CUDA backend was not built")
+def test_full_width_denoise_matches_reference_cuda_backend(pkg):
+    """4 blocks x 4 Euler steps at hidden 5376 / 56 heads / FFN 14336, S = 1,664 (config-1 rows)."""
+    case = make_denoise_case(rows=1664, text_rows=128, heads=56, hidden=5376, ffn=14336, blocks=4,
+                             steps=4, seed=1, fast=True, sigmas=pkg.serving_sigmas(4))
+    out = {}
+    for name, path in (("b200", None), ("reference", REF_CUDA)):
+        gpu = pkg.Gpu(0, lib_path=path)
+        try:
+            out[name], _ = gpu_denoise(pkg, gpu, case)
+        finally:
+            gpu.close()
+    cos, r = cosine(out["b200"], out["reference"]), rel_l2(out["b200"], out["reference"])
+    print(f"full-width 4x4 denoise vs reference CUDA backend: cosine={cos:.7f} rel_l2={r:.3e}")
+    assert cos >= 0.999
+    assert rel_l2(out["reference"], case.latent) > 0.05

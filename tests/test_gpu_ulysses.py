@@ -34,3 +34,19 @@ def test_sharded_block_matches_oracle(rows, mode):
     print(res.stdout[-2000:])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert "PASS" in res.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_guidance_groups_match_oracle(world):
+    """Classifier-free guidance over two groups of world/2 ranks (tests/cfg_worker.py)."""
+    if gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    port = 29300 + os.getpid() % 300
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                          f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                          "--master-port", str(port), str(ROOT / "tests" / "cfg_worker.py")],
+                         capture_output=True, text=True, timeout=600, env=env)
+    print(res.stdout[-2000:])
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "PASS" in res.stdout

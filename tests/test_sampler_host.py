@@ -1,0 +1,129 @@
+"""Host logic of the Euler sampler, no GPU: the sigma schedule against the reference's
+known-answer checks (tests/test_h3.c:101-124) and the op sequence of the three guidance modes
+against a recording stand-in for the device context."""
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import __graft_entry__ as entry
+    return entry.load_package()
+
+
+def test_serving_sigmas_known_answers(pkg):
+    s50 = pkg.serving_sigmas(50)
+    assert s50[0] == 1.0 and s50[50] == 0.0
+    assert abs(s50[25] - np.float32(12.0 * 0.5 / (1.0 + 11.0 * 0.5))) <= 1e-7
+    assert np.all(np.diff(s50) < 0)
+    s4 = pkg.serving_sigmas(4)
+    assert s4[0] == 1.0 and s4[4] == 0.0
+    assert abs(s4[1] - 36.0 / 37.0) <= 1e-7
+    a4 = pkg.serving_sigmas(4, shift=3.0)      # the audio stream's shift (h3_host.h:13)
+    assert abs(a4[1] - 9.0 / 10.0) <= 1e-7
+    assert np.all(np.diff(a4) < 0)
+
+
+class FakeTensor:
+    def __init__(self, name):
+        self.name = name
+
+
+class FakeGpu:
+    def __init__(self):
+        self.log = []
+
+    def new(self, n, dtype):
+        return FakeTensor(f"new{n}")
+
+    def begin(self):
+        self.log.append("begin")
+
+    def submit(self):
+        self.log.append("submit")
+
+    def flush(self):
+        self.log.append("flush")
+
+    def op(self, name, *args):
+        self.log.append((name,) + tuple(a.name if isinstance(a, FakeTensor) else a for a in args))
+
+
+class FakeStep:
+    """Stands in for DenoiseStep: records which text and row maps each forward used."""
+
+    def __init__(self, gpu, pkg):
+        class D:
+            pass
+        self.dit = D()
+        self.dit.gpu, self.dit.s = gpu, pkg.DitShape()
+        self.video_rows = 10
+        self.text_hidden = FakeTensor("cond_text")
+        self.velocity = FakeTensor("velocity")
+        self.row_map = self.final_row_map = None
+
+    def forward(self):
+        self.dit.gpu.log.append(("forward", self.text_hidden.name, self.row_map.name, self.final_row_map.name))
+
+    def euler(self, delta):
+        self.dit.gpu.log.append(("euler", round(delta, 6)))
+
+
+def maps(n):
+    return [FakeTensor(f"rm{i}") for i in range(n)], [FakeTensor(f"frm{i}") for i in range(n)]
+
+
+def test_plain_loop(pkg):
+    gpu = FakeGpu()
+    step = FakeStep(gpu, pkg)
+    sig = np.array([1.0, 0.5, 0.0], np.float32)
+    pkg.EulerSampler(step, sig, *maps(2)).run()
+    assert gpu.log == ["begin", ("forward", "cond_text", "rm0", "frm0"), ("euler", 0.5), "flush",
+                       ("forward", "cond_text", "rm1", "frm1"), ("euler", 0.5), "submit"]
+
+
+def test_sequential_guidance(pkg):
+    gpu = FakeGpu()
+    step = FakeStep(gpu, pkg)
+    sig = np.array([1.0, 0.0], np.float32)
+    pkg.EulerSampler(step, sig, *maps(1), guidance=2.5, uncond_text=FakeTensor("uncond_text")).run()
+    assert gpu.log == ["begin", ("forward", "cond_text", "rm0", "frm0"),
+                       ("copy_bf16", "new960", 0, "velocity", 0, 960),
+                       ("forward", "uncond_text", "rm0", "frm0"),
+                       ("h3x_cfg_combine_bf16", "velocity", "new960", "velocity", 960, 2.5),
+                       ("euler", 1.0), "submit"]
+    assert step.text_hidden.name == "cond_text"
+
+
+@pytest.mark.parametrize("is_cond", [True, False])
+def test_paired_guidance(pkg, is_cond):
+    gpu = FakeGpu()
+    step = FakeStep(gpu, pkg)
+
+    class Pair:
+        def swap(self, out, inp):
+            gpu.log.append(("swap", out.name, inp.name))
+    pair = Pair()
+    pair.is_cond = is_cond
+    pkg.EulerSampler(step, np.array([1.0, 0.0], np.float32), *maps(1), guidance=4.0, pair=pair).run()
+    combine = ("h3x_cfg_combine_bf16", "velocity") + (("velocity", "new960") if is_cond else ("new960", "velocity")) + (960, 4.0)
+    assert gpu.log == ["begin", ("forward", "cond_text", "rm0", "frm0"), ("swap", "new960", "velocity"),
+                       combine, ("euler", 1.0), "submit"]
+
+
+def test_guidance_needs_one_source(pkg):
+    gpu = FakeGpu()
+    with pytest.raises(ValueError):
+        pkg.EulerSampler(FakeStep(gpu, pkg), np.array([1.0, 0.0], np.float32), *maps(1), guidance=2.0)
+
+
+def test_cfg_combine_oracle_formula():
+    import h3_oracle as o
+    rng = np.random.default_rng(0)
+    c = o.to_bf16(rng.standard_normal(1000, dtype=np.float32))
+    u = o.to_bf16(rng.standard_normal(1000, dtype=np.float32))
+    got = o.from_bf16(o.cfg_combine_bf16(c, u, 3.0))
+    cf, uf = o.from_bf16(c).astype(np.float64), o.from_bf16(u).astype(np.float64)
+    want = uf + 3.0 * (cf - uf)
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -8 + 1e-30)
+    assert np.array_equal(o.cfg_combine_bf16(c, u, 1.0), c)     # guidance 1 returns cond exactly
