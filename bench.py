@@ -230,7 +230,7 @@ class TorchMemory:
             class _Span:
                 __cuda_array_interface__ = {
                     "shape": (tensor.elements * size,), "version": 2, "typestr": "|u1",
-                    "data": (tensor.pointer(), False)}
+                    "data": (tensor.pointer, False)}
             view = self.torch.as_tensor(_Span(), device=self.device)
             self.by_handle[tensor.handle] = view
         return self.by_handle[tensor.handle]
@@ -376,12 +376,12 @@ def run_gpu_arm(args, shape, sequence, text_rows):
     gpu = pkg.Gpu(local_rank)          # raises if the CUDA library or the device is missing
     mem = TorchMemory(torch, pkg, gpu, device)
     exchange = None
-    if world > 1 and args.exchange == "push":
+    if world > 1 and args.exchange in ("push", "loopback"):
         def gather(obj):
             out = [None] * world
             dist.all_gather_object(out, obj)
             return out
-        exchange = pkg.PeerExchange(gpu, world, rank, gather)
+        exchange = pkg.PeerExchange(gpu, world, rank, gather, loopback=args.exchange == "loopback")
     elif world > 1:
         exchange = NcclExchange(dist, mem, world, rank)
     peaks = measured_peaks()
@@ -529,8 +529,11 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         if isinstance(exchange, NcclExchange):
             line["all_to_all_calls_per_step"] = exchange.calls // max(1, (args.warmup + 2 * args.steps + 1))
         if world > 1:
-            line["config"]["exchange"] = ("peer stores from the QKV and attention epilogues + 2 flag barriers per block"
-                                          if dit.push else "pack + NCCL all-to-all + unpack")
+            line["config"]["exchange"] = {
+                "push": "peer stores from the QKV and attention epilogues + 2 flag barriers per block",
+                "loopback": "MEASUREMENT AID, results invalid: peer stores redirected to local memory, no barriers "
+                            "(step time without any exchange cost)",
+                "nccl": "pack + NCCL all-to-all + unpack"}[args.exchange]
     if world > 1:
         dist.barrier()
         if dit.push:
@@ -672,8 +675,10 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=50)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
-                    help="N>1: peer stores fused into the kernels, or pack + NCCL all-to-all + unpack")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl", "loopback"],
+                    help="N>1: peer stores fused into the kernels, or pack + NCCL all-to-all + unpack; "
+                         "loopback = same kernels with the stores kept local and no barriers, to "
+                         "measure the exposed cost of the exchange (results invalid)")
     ap.add_argument("--euler-steps", type=int, default=20, help="c5: Euler steps per denoise")
     ap.add_argument("--guidance", type=float, default=5.0,
                     help="c5: guidance scale (the reference has no guidance pass; harness parameter)")

@@ -19,8 +19,12 @@ class PeerExchange:
 
     all_gather(obj) -> list of every rank's obj, in rank order (a host-side collective)."""
 
-    def __init__(self, gpu: Gpu, world: int, rank: int, all_gather):
-        self.gpu, self.world, self.rank = gpu, world, rank
+    def __init__(self, gpu: Gpu, world: int, rank: int, all_gather, loopback: bool = False):
+        """loopback=True is a measurement aid: every peer entry points at this rank's own
+        buffers and the barriers are skipped, so a step moves the same bytes with no NVLink
+        traffic and no waiting (results are meaningless); step time minus the loopback step
+        time is the exposed cost of the exchange."""
+        self.gpu, self.world, self.rank, self.loopback = gpu, world, rank, loopback
         self._all_gather = all_gather
         self._blocks: list[int] = []
         self._mapped: list[int] = []
@@ -35,6 +39,8 @@ class PeerExchange:
         if not block:
             raise H3Error(f"h3x_peer_alloc failed: {gpu.error()}")
         self._blocks.append(block)
+        if self.loopback:
+            return [block] * self.world
         handles = self._all_gather(bytes(handle))
         out = []
         for r, h in enumerate(handles):
@@ -64,7 +70,8 @@ class PeerExchange:
         return local
 
     def barrier(self) -> None:
-        self.gpu.op("h3x_peer_barrier", self.peers)
+        if not self.loopback:
+            self.gpu.op("h3x_peer_barrier", self.peers)
 
     def close(self) -> None:
         lib, gpu = self.gpu.lib, self.gpu
