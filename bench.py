@@ -387,6 +387,11 @@ def run_gpu_arm(args, shape, sequence, text_rows):
     peaks = measured_peaks()
 
     dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
+    if world > 1 and args.exchange == "loopback":
+        # the slots other ranks would fill must not stay zero: attention's cost and power draw
+        # depend on the data (rescale decisions, switching activity)
+        for t in dit.gathered:
+            mem.torch_of(t).view(torch.bfloat16).normal_(0.0, 1.0)
     s = shape
     n_latent = max(1, step.video_rows) * s.video_patch
     host_latent = torch.randn(n_latent, dtype=torch.float32).pin_memory()

@@ -619,38 +619,69 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         /* total row sum = sum of the two halves' partial sums (same reference maximum) */
         if (alive) *mine = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        if (alive && mbar_wait(o_done, 0, stop)) {
+        /* Epilogue. Every MMA of the CTA has completed once o_done fires, so the Q tiles'
+         * shared memory is free: the two warps that share 32 rows stage their halves of the
+         * normalised output there (16-byte chunks, chunk index XOR row: no bank conflicts on
+         * either side) and then write whole 256-byte rows, two rows per store instruction.
+         * Full-line stores matter when the destination is another GPU's memory. */
+        const bool finished = alive && mbar_wait(o_done, 0, stop);
+        const uint32_t stage = q_smem + (tile * 4 + quarter) * 8192;
+        if (finished) {
             tc_fence_after();
             const float inv = 1.0f / (l_run + *theirs);
-            uint16_t *dst;
-            if (PUSH) {
-                const uint32_t owner = min(row / args.rows_local, args.world - 1);
-                uint16_t *base = args.peer_o[0];
-#pragma unroll
-                for (uint32_t r = 1; r < 8; r++)
-                    if (r == owner) base = args.peer_o[r];
-                dst = base +
-                      (size_t(row - owner * args.rows_local) * args.heads_total + args.head0 + head) * AT_D;
-            } else {
-                dst = args.head_major ? args.out + (size_t(head) * args.seq + row) * AT_D
-                                      : args.out + (size_t(row) * args.heads + head) * AT_D;
-            }
-            dst += half * 64;
 #pragma unroll 1
-            for (int c = 0; c < 2; c++) {
+            for (uint32_t c = 0; c < 2; c++) {
                 uint32_t o[32];
                 tmem_ld32(tmem_o + half * 64 + c * 32, o);
                 tmem_ld_wait();
-                if (row < args.seq) {
 #pragma unroll
-                    for (int v = 0; v < 4; v++) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                        *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = w;
+                for (uint32_t v = 0; v < 4; v++) {
+                    const uint32_t chunk = half * 8 + c * 4 + v;
+                    const uint32_t addr = stage + lane * 256 + ((chunk ^ (lane & 15)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv)),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv)),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv)),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv))
+                                 : "memory");
+                }
+            }
+        }
+        uint32_t both_finished;
+        asm volatile(
+            "{\n\t.reg .pred pin, pout;\n\t"
+            "setp.ne.u32 pin, %2, 0;\n\t"
+            "bar.red.and.pred pout, %1, 64, pin;\n\t"
+            "selp.u32 %0, 1, 0, pout;\n\t}"
+            : "=r"(both_finished)
+            : "r"(pair_barrier), "r"(uint32_t(finished))
+            : "memory");
+        if (both_finished) {
+            const uint32_t row0 = q_block * AT_Q + tile * AT_QT + quarter * 32;
+            const uint32_t chunk = lane & 15;
+#pragma unroll 1
+            for (uint32_t j = 0; j < 8; j++) {
+                const uint32_t r = half * 16 + 2 * j + (lane >> 4);
+                const uint32_t out_row = row0 + r;
+                uint4 val;
+                const uint32_t addr = stage + r * 256 + ((chunk ^ (r & 15)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr) : "memory");
+                if (out_row < args.seq) {
+                    uint16_t *dst;
+                    if (PUSH) {
+                        const uint32_t owner = min(out_row / args.rows_local, args.world - 1);
+                        uint16_t *peer = args.peer_o[0];
+#pragma unroll
+                        for (uint32_t p = 1; p < 8; p++)
+                            if (p == owner) peer = args.peer_o[p];
+                        dst = peer + (size_t(out_row - owner * args.rows_local) * args.heads_total +
+                                      args.head0 + head) * AT_D;
+                    } else {
+                        dst = args.head_major ? args.out + (size_t(head) * args.seq + out_row) * AT_D
+                                              : args.out + (size_t(out_row) * args.heads + head) * AT_D;
                     }
+                    *reinterpret_cast<uint4 *>(dst + chunk * 8) = val;
                 }
             }
         }
