@@ -316,6 +316,31 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+/* 8-column forms for the rare rescale of O, which runs while the scores occupy the registers */
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                   "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+                   "r"(r[7])
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -359,8 +384,8 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const uint32_t v_full = k_empty + 8 * AT_K_STAGES;     /* AT_V_STAGES */
     const uint32_t v_empty = v_full + 8 * AT_V_STAGES;     /* AT_V_STAGES */
     const uint32_t s_full = v_empty + 8 * AT_V_STAGES;     /* [tile] = 2  */
-    const uint32_t p_full = s_full + 16;                   /* [tile] = 2  */
-    const uint32_t o_done = p_full + 16;                   /* 1           */
+    const uint32_t p_full = s_full + 16;                   /* [tile][early, late] = 4 */
+    const uint32_t o_done = p_full + 32;                   /* 1           */
     const uint32_t tmem_holder = o_done + 8;
     volatile int *stop = reinterpret_cast<volatile int *>(at_smem + (tmem_holder + 8 - base));
 
@@ -385,7 +410,8 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         }
         for (int t = 0; t < AT_TILES; t++) {
             mbar_init(s_full + 8 * t, 1);
-            mbar_init(p_full + 8 * t, 8);
+            mbar_init(p_full + 16 * t, 8);
+            mbar_init(p_full + 16 * t + 8, 8);
         }
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -462,7 +488,10 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 AT_TRACE(0, j, 0);
 #pragma unroll
                 for (int t = 0; t < AT_TILES; t++) {
-                    alive = __all_sync(0xffffffffu, mbar_wait(p_full + 8 * t, j & 1, stop));
+                    /* P_t arrives in two parts: each softmax warp publishes the first 32 of its
+                     * 64 keys while it still works on the rest, so the first half of O_t += P_t.V_j
+                     * (16-key groups 0,1 and 4,5) overlaps the second half of the exponentials */
+                    alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t, j & 1, stop));
                     if (alive && t == 0)
                         alive = __all_sync(0xffffffffu, mbar_wait(v_full + 8 * vs, vp, stop));
                     if (!alive) break;
@@ -474,9 +503,16 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     const uint32_t a = tmem_base + AT_COL_S + t * AT_KV;
                     if (j == 0) umma_ts<false>(d, a, v_lo, idesc_pv, leader);
                     else umma_ts<true>(d, a, v_lo, idesc_pv, leader);
-#pragma unroll
-                    for (int kk = 1; kk < AT_KV / 16; kk++)
-                        umma_ts<true>(d, a + kk * 8, v_lo + kk * (2048 >> 4), idesc_pv, leader);
+                    umma_ts<true>(d, a + 1 * 8, v_lo + 1 * (2048 >> 4), idesc_pv, leader);
+                    umma_ts<true>(d, a + 4 * 8, v_lo + 4 * (2048 >> 4), idesc_pv, leader);
+                    umma_ts<true>(d, a + 5 * 8, v_lo + 5 * (2048 >> 4), idesc_pv, leader);
+                    alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t + 8, j & 1, stop));
+                    if (!alive) break;
+                    tc_fence_after();
+                    umma_ts<true>(d, a + 2 * 8, v_lo + 2 * (2048 >> 4), idesc_pv, leader);
+                    umma_ts<true>(d, a + 3 * 8, v_lo + 3 * (2048 >> 4), idesc_pv, leader);
+                    umma_ts<true>(d, a + 6 * 8, v_lo + 6 * (2048 >> 4), idesc_pv, leader);
+                    umma_ts<true>(d, a + 7 * 8, v_lo + 7 * (2048 >> 4), idesc_pv, leader);
                     if (t == AT_TILES - 1) umma_commit_if(v_empty + 8 * vs, leader);
                     if (more) {
                         /* the next scores of this tile go straight behind: in-order execution keeps
@@ -512,7 +548,7 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         const uint32_t tmem_s = tmem_base + AT_COL_S + tile * AT_KV + half * 64 + lane_base;
         const uint32_t tmem_p = tmem_base + AT_COL_S + tile * AT_KV + half * 32 + lane_base;
         const uint32_t tmem_o = tmem_base + AT_COL_O + tile * AT_D + lane_base;
-        const uint32_t my_s_full = s_full + 8 * tile, my_p_full = p_full + 8 * tile;
+        const uint32_t my_s_full = s_full + 8 * tile, my_p_full = p_full + 16 * tile;
         const uint32_t pair_barrier = 1 + tile * 4 + quarter;          /* 64 threads each */
         float *xchg = reinterpret_cast<float *>(at_smem + (bars - base) + AT_BAR_BYTES);
         float *mine = xchg + (tile * 2 + half) * AT_QT + local_row;
@@ -542,13 +578,14 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     if (k0 + 32 + i >= valid) s1[i] = 0xff800000u;
                 }
             }
+            /* three-input max: half the instructions of a pairwise reduction */
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(s0[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(s1[i]));
-                mx3 = fmaxf(mx3, __uint_as_float(s1[i + 1]));
+            for (int i = 0; i < 32; i += 4) {
+                mx0 = max3_f32(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+                mx1 = max3_f32(mx1, __uint_as_float(s0[i + 2]), __uint_as_float(s0[i + 3]));
+                mx2 = max3_f32(mx2, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                mx3 = max3_f32(mx3, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
             }
             const float mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             *mine = mx_half;
@@ -576,44 +613,60 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 m_run = m_tile;
                 rescale = true;
             }
-            const float neg_m = -m_run;
-            float sum0 = 0.0f, sum1 = 0.0f;
-            uint32_t packed[32];
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(s0[2 * i]), scale_log2, neg_m));
-                float p1 = fast_exp2(fmaf(__uint_as_float(s0[2 * i + 1]), scale_log2, neg_m));
-                float p2 = fast_exp2(fmaf(__uint_as_float(s1[2 * i]), scale_log2, neg_m));
-                float p3 = fast_exp2(fmaf(__uint_as_float(s1[2 * i + 1]), scale_log2, neg_m));
-                sum0 += p0 + p1;
-                sum1 += p2 + p3;
-                packed[i] = pack_bf16(p0, p1);
-                packed[16 + i] = pack_bf16(p2, p3);
-            }
-            l_run = l_run * alpha + (sum0 + sum1);
-            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 3);
-
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
                 /* O_t is stable: P.V of tile j-1 finished before S_t(j) was signalled. Each
                  * key half rescales its own 64 columns of O_t (the decision is identical in
-                 * both warps of a row: same maxima, same history). */
+                 * both warps of a row: same maxima, same history). Done before any part of
+                 * P_t(j) is published, so no P.V of this step can run ahead of it. */
 #pragma unroll 1
-                for (int c = 0; c < 2; c++) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem_o + half * 64 + c * 32, o);
+                for (int c = 0; c < 8; c++) {
+                    uint32_t o[8];
+                    tmem_ld8(tmem_o + half * 64 + c * 8, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
+                    for (int i = 0; i < 8; i++)
                         o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(tmem_o + half * 64 + c * 32, o);
+                    tmem_st8(tmem_o + half * 64 + c * 8, o);
                 }
             }
-            /* keys 64*half + 2i, +1 -> P column 32*half + i */
-            tmem_st32(tmem_p, packed);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(my_p_full);
+            /* x = s * scale_log2 - m and the row sum run as packed F32 pairs (one instruction
+             * per two elements); the exponential itself is scalar (MUFU). The thread's first 32
+             * keys are published as soon as they are done (keys 64*half + 2i, +1 -> P column
+             * 32*half + i), the other 32 follow. */
+            const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+            const uint64_t neg_m2 = pack_f32x2(-m_run, -m_run);
+            uint64_t sum_a = 0, sum_b = 0;                  /* two packed partial sums (+0.0f) */
+#pragma unroll
+            for (int part = 0; part < 2; part++) {
+                const uint32_t(&sv)[32] = part == 0 ? s0 : s1;
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(sv[4 * i]), __uint_as_float(sv[4 * i + 1])),
+                                                  scale2, neg_m2);
+                    const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(sv[4 * i + 2]), __uint_as_float(sv[4 * i + 3])),
+                                                  scale2, neg_m2);
+                    float x0, x1, x2, x3;
+                    unpack_f32x2(xa, x0, x1);
+                    unpack_f32x2(xb, x2, x3);
+                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                    const float p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+                    sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
+                    sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
+                    packed[2 * i] = pack_bf16(p0, p1);
+                    packed[2 * i + 1] = pack_bf16(p2, p3);
+                }
+                tmem_st16(tmem_p + part * 16, packed);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(my_p_full + 8 * part);
+                if (part == 0 && quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 3);
+            }
+            float sum0, sum1, sum2, sum3;
+            unpack_f32x2(sum_a, sum0, sum1);
+            unpack_f32x2(sum_b, sum2, sum3);
+            l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
             if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 4);
         }
         /* total row sum = sum of the two halves' partial sums (same reference maximum) */
