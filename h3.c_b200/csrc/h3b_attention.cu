@@ -296,6 +296,8 @@ struct AttnArgs {
      * [rows_local][heads_total][128] at head head0 + head */
     uint32_t world, rows_local, heads_total, head0;
     uint16_t *peer_o[8];
+    /* block-sparse mask: per-CTA step lists (see h3_gpu); NULL = dense */
+    const uint32_t *sparse_cta_ptr, *sparse_steps;
     long long *trace;   /* optional [role][tile][event] clock64 stamps of CTA (0,0); NULL = off */
 };
 
@@ -368,7 +370,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
  * swizzle and read as an N-major B operand: along N, 64-element groups are one box
  * (16384 bytes) apart = leading byte offset; along K, groups of 8 keys are 1024 bytes
  * apart = stride byte offset; 16 keys (one instruction) are 2048 bytes. */
-template <bool PUSH>
+template <bool PUSH, bool SPARSE>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
@@ -391,7 +393,15 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_block = blockIdx.x, head = blockIdx.y;
-    const uint32_t n_tiles = (args.seq + AT_KV - 1) / AT_KV;
+    /* dense: key tiles 0 .. n_tiles-1 in order; sparse: this CTA's step list (never longer than
+     * the dense walk, so no defect in the lists can unbound the loops) */
+    uint32_t n_tiles = (args.seq + AT_KV - 1) / AT_KV;
+    const uint32_t *steps = nullptr;
+    if (SPARSE) {
+        const uint32_t first = args.sparse_cta_ptr[q_block];
+        steps = args.sparse_steps + first;
+        n_tiles = min(n_tiles, args.sparse_cta_ptr[q_block + 1] - first);
+    }
 
     if ((base & 1023u) != 0) {  /* swizzled tiles need 1024-byte alignment */
         if (threadIdx.x == 0) atomicMax(args.status, int(H3B_STATUS_ATTN_TIMEOUT));
@@ -434,7 +444,7 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
             tma_load_3d(q_smem + AT_Q_BYTES / 2, &map_q, q_full, 64, int(head), int(q_block * AT_Q));
             uint32_t ks = 0, kp = 0, vs = 0, vp = 0;
             for (uint32_t j = 0; j < n_tiles; j++) {
-                const int row0 = int(j * AT_KV);
+                const int row0 = int((SPARSE ? (steps[j] & 0x0fffffffu) : j) * AT_KV);
                 if (!mbar_wait(k_empty + 8 * ks, kp ^ 1, stop)) break;
                 mbar_expect_tx(k_full + 8 * ks, AT_K_BYTES);
                 tma_load_3d(k_smem + ks * AT_K_BYTES, &map_k, k_full + 8 * ks, 0, int(head), row0);
@@ -569,7 +579,11 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
             tmem_ld32(tmem_s, s0);
             tmem_ld32(tmem_s + 32, s1);
             tmem_ld_wait();
-            const uint32_t valid = args.seq - j * AT_KV;   /* >= 1; < 128 only on the last tile */
+            /* keys of the tile this warp may use: all but the ragged tail of the sequence; none
+             * when the block-sparse mask leaves out this (query block, 64-key half) */
+            const uint32_t step = SPARSE ? steps[j] : (j | 0xf0000000u);
+            const uint32_t valid =
+                ((step >> (28 + 2 * tile + half)) & 1u) ? args.seq - (step & 0x0fffffffu) * AT_KV : 0u;
             if (valid < uint32_t(AT_KV)) {
                 const uint32_t k0 = half * 64;
 #pragma unroll
@@ -634,7 +648,10 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
              * keys are published as soon as they are done (keys 64*half + 2i, +1 -> P column
              * 32*half + i), the other 32 follow. */
             const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
-            const uint64_t neg_m2 = pack_f32x2(-m_run, -m_run);
+            /* m_run is still -inf only when every score so far was masked: subtract 0 then, so
+             * that the masked scores give 2^-inf = 0 and not 2^(inf - inf) */
+            const float neg_m = m_run == -INFINITY ? 0.0f : -m_run;
+            const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
             uint64_t sum_a = 0, sum_b = 0;                  /* two packed partial sums (+0.0f) */
 #pragma unroll
             for (int part = 0; part < 2; part++) {
@@ -789,13 +806,20 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
                    h3b_aligned16(value->data) && (!output || h3b_aligned16(output->data));
     if (peers && !(hd == AT_D && aligned && scale > 0.0f))
         return h3b_fail(gpu, "the push variant of SDPA needs head_dim 128 and aligned tensors");
+    /* a registered block-sparse mask applies to calls with its row count (reference
+     * h3_cuda_attention.cu:2559-2562); only the tensor-core kernel walks it */
+    const bool sparse = gpu->sparse_cta_ptr && gpu->sparse_rows == seq;
+    if (sparse && !(hd == AT_D && aligned && !simt && scale > 0.0f))
+        return h3b_fail(gpu, "the block-sparse mask needs head_dim 128, aligned tensors and the tensor-core kernel");
     if (hd == AT_D && aligned && !simt && scale > 0.0f) {
         static bool configured = false;
         if (!configured) {
-            if (cudaFuncSetAttribute(h3b_sdpa_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     int(AT_SMEM)) != cudaSuccess ||
-                cudaFuncSetAttribute(h3b_sdpa_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     int(AT_SMEM)) != cudaSuccess) {
+            bool ok = true;
+            for (auto *kernel : {h3b_sdpa_tc<false, false>, h3b_sdpa_tc<false, true>,
+                                 h3b_sdpa_tc<true, false>, h3b_sdpa_tc<true, true>})
+                ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                int(AT_SMEM)) == cudaSuccess;
+            if (!ok) {
                 cudaGetLastError();
                 return h3b_fail(gpu, "cannot reserve shared memory for the attention kernel");
             }
@@ -816,6 +840,10 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
             for (uint32_t r = 0; r < peers->world; r++)
                 args.peer_o[r] = static_cast<uint16_t *>(peers->o[r]);
         }
+        if (sparse) {
+            args.sparse_cta_ptr = gpu->sparse_cta_ptr;
+            args.sparse_steps = gpu->sparse_steps;
+        }
         args.status = gpu->status_device;
         args.seq = seq;
         args.heads = heads;
@@ -824,8 +852,9 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         args.trace = nullptr;
         if (const char *t = getenv("H3B_ATTN_TRACE_PTR")) args.trace = reinterpret_cast<long long *>(strtoull(t, nullptr, 0));
         dim3 grid((seq + AT_Q - 1) / AT_Q, heads);
-        if (peers) h3b_sdpa_tc<true><<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
-        else h3b_sdpa_tc<false><<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
+        auto *kernel = peers ? (sparse ? h3b_sdpa_tc<true, true> : h3b_sdpa_tc<true, false>)
+                             : (sparse ? h3b_sdpa_tc<false, true> : h3b_sdpa_tc<false, false>);
+        kernel<<<grid, AT_THREADS, AT_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
         return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
     }
     if (hd > uint32_t(kSimtThreads * kSimtMaxDimsPerThread))

@@ -67,8 +67,13 @@ struct h3_gpu {
     int *status_device = nullptr;   /* kernel status word */
     int status_seen = 0;
 
-    /* block-sparse attention mask registration (kept for API parity) */
+    /* Block-sparse attention mask (h3_gpu_sdpa_set_sparse), regrouped for the tensor-core
+     * kernel: one list per CTA (256 query rows = two 128-row query blocks) of steps over
+     * 128-key tiles; a step word = key tile index | 4 mask bits << 28, bit 2*t + h set when
+     * query block t of the CTA attends the 64-key half h of the tile. */
     uint32_t sparse_rows = 0;
+    uint32_t *sparse_cta_ptr = nullptr;   /* device, ctas + 1 offsets */
+    uint32_t *sparse_steps = nullptr;     /* device */
 
     char profile_label[128] = {0};
     double profile_mark = 0.0;

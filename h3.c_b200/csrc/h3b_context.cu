@@ -13,6 +13,8 @@
  */
 #include "h3b_common.cuh"
 
+#include <algorithm>
+
 #include <cerrno>
 #include <cstdlib>
 #include <ctime>
@@ -198,6 +200,8 @@ extern "C" void h3_gpu_free(h3_gpu *gpu) {
         if (slot.done) cudaEventDestroy(slot.done);
     }
     if (gpu->status_device) cudaFree(gpu->status_device);
+    if (gpu->sparse_cta_ptr) cudaFree(gpu->sparse_cta_ptr);
+    if (gpu->sparse_steps) cudaFree(gpu->sparse_steps);
     delete gpu;
 }
 
@@ -296,14 +300,59 @@ extern "C" void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase) {
     gpu->profile_mark = now;
 }
 
-extern "C" int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t, const uint32_t *,
-                                      size_t, uint32_t) {
+static void sparse_clear(h3_gpu *gpu) {
+    if (gpu->sparse_cta_ptr) cudaFree(gpu->sparse_cta_ptr);
+    if (gpu->sparse_steps) cudaFree(gpu->sparse_steps);
+    gpu->sparse_cta_ptr = gpu->sparse_steps = nullptr;
+    gpu->sparse_rows = 0;
+}
+
+/* Register / clear the block-sparse mask (reference h3_cuda_attention.cu:1812-1857: same
+ * validation, same "applies to calls whose row count equals rows"). The CSR over 64-key tiles
+ * per 128-row query block is regrouped on the host into per-CTA step lists over 128-key tiles
+ * (see h3_gpu in h3b_common.cuh): the union of the two query blocks' lists, ascending, with
+ * the per-(query block, 64-key half) bits. A tile listed twice for a block counts once (the
+ * reference kernel would visit it twice; its own mask builder lists each tile once). */
+extern "C" int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t ptr_count,
+                                      const uint32_t *idx, size_t idx_count, uint32_t rows) {
     if (!gpu) return 0;
-    if (!ptr) {
-        gpu->sparse_rows = 0;
-        return 1;
+    cudaDeviceSynchronize();   /* no attention call may still read the lists being replaced */
+    sparse_clear(gpu);
+    if (!ptr) return 1;
+    if (!idx || !ptr_count || !idx_count || !rows) return 0;
+    const uint32_t key_tiles64 = (rows + 63) / 64, query_blocks = (rows + 127) / 128;
+    if (ptr[0] != 0 || ptr[ptr_count - 1] != uint32_t(idx_count)) return 0;
+    for (size_t i = 1; i < ptr_count; i++)
+        if (ptr[i] < ptr[i - 1]) return 0;
+    for (size_t i = 0; i < idx_count; i++)
+        if (idx[i] >= key_tiles64) return 0;
+    const uint32_t listed_blocks = uint32_t(ptr_count - 1);
+    const uint32_t ctas = (query_blocks + 1) / 2, key_tiles128 = (rows + 127) / 128;
+    std::vector<uint32_t> cta_ptr(ctas + 1, 0), steps;
+    std::vector<uint8_t> bits(key_tiles128);
+    for (uint32_t c = 0; c < ctas; c++) {
+        std::fill(bits.begin(), bits.end(), uint8_t(0));
+        for (uint32_t t = 0; t < 2; t++) {
+            const uint32_t block = 2 * c + t;
+            if (block >= listed_blocks) continue;
+            for (uint32_t e = ptr[block]; e < ptr[block + 1]; e++)
+                bits[idx[e] >> 1] |= uint8_t(1u << (2 * t + (idx[e] & 1u)));
+        }
+        for (uint32_t k = 0; k < key_tiles128; k++)
+            if (bits[k]) steps.push_back(k | (uint32_t(bits[k]) << 28));
+        if (steps.size() == cta_ptr[c]) steps.push_back(0);   /* nothing listed: one all-masked step */
+        cta_ptr[c + 1] = uint32_t(steps.size());
     }
-    return h3b_fail(gpu, "block-sparse attention masks are not supported by this backend");
+    if (cudaMalloc(reinterpret_cast<void **>(&gpu->sparse_cta_ptr), cta_ptr.size() * 4) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void **>(&gpu->sparse_steps), steps.size() * 4) != cudaSuccess ||
+        cudaMemcpy(gpu->sparse_cta_ptr, cta_ptr.data(), cta_ptr.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(gpu->sparse_steps, steps.data(), steps.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        sparse_clear(gpu);
+        return h3b_fail(gpu, "cannot upload the block-sparse attention mask");
+    }
+    gpu->sparse_rows = rows;
+    return 1;
 }
 
 /* -------------------------------------------------------------- tensors */

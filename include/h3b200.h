@@ -55,6 +55,11 @@ int h3_gpu_is_m5(const h3_gpu *gpu);                /* 0 */
 int h3_gpu_has_nax_mlp(const h3_gpu *gpu);          /* 0 */
 int h3_gpu_has_int8_mlp(const h3_gpu *gpu);         /* 0 */
 int h3_gpu_prefers_gpu_sampler(const h3_gpu *gpu);  /* 1 */
+/* Block-sparse attention mask (h3_gpu.h:44-51, h3_cuda_attention.cu:1812-1857): CSR over
+ * 64-row K/V tiles per 128-row query block, applied to head_dim-128 attention calls whose row
+ * count equals rows (other calls stay dense); NULL ptr clears; same validation as the
+ * reference. The lists are regrouped for the 256-row x 128-key tiles of the tensor-core
+ * kernel; a tile listed twice for one block counts once. */
 int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t ptr_count,
                            const uint32_t *idx, size_t idx_count, uint32_t rows);
 int h3_gpu_begin(h3_gpu *gpu);

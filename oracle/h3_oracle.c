@@ -463,10 +463,15 @@ void h3o_qkv_rope_bf16(uint16_t *q, uint16_t *k, uint16_t *v,
         }
 }
 
-void h3o_sdpa_bf16_rows(uint16_t *out, const uint16_t *q, const uint16_t *k,
-                        const uint16_t *v, uint32_t seq, uint32_t heads,
-                        uint32_t hd, float scale, int head_major, int round_p,
-                        uint32_t row_begin, uint32_t row_end) {
+/* sparse_ptr/sparse_idx: optional block-sparse mask in the form h3_gpu_sdpa_set_sparse takes
+ * (h3_gpu.h:44-51; walked by the reference kernel at h3_cuda_attention.cu:1652-1673): CSR over
+ * 64-key tiles per 128-row query block; a query row attends exactly the keys of its block's
+ * listed tiles. NULL = dense. */
+static void sdpa_core(uint16_t *out, const uint16_t *q, const uint16_t *k,
+                      const uint16_t *v, uint32_t seq, uint32_t heads,
+                      uint32_t hd, float scale, int head_major, int round_p,
+                      uint32_t row_begin, uint32_t row_end,
+                      const uint32_t *sparse_ptr, const uint32_t *sparse_idx) {
     if (!seq || !heads || !hd || row_begin >= row_end) return;
     uint32_t padded = (seq + 15u) & ~15u;
 #pragma omp parallel
@@ -476,6 +481,7 @@ void h3o_sdpa_bf16_rows(uint16_t *out, const uint16_t *q, const uint16_t *k,
         float *vf = (float *)aligned_alloc(64, (size_t)padded * hd * 4);
         float *scores = (float *)aligned_alloc(64, (size_t)padded * 4);
         float *acc = (float *)aligned_alloc(64, ((size_t)hd * 4 + 63) & ~(size_t)63);
+        unsigned char *keep = (unsigned char *)malloc(padded);
 #pragma omp for schedule(dynamic, 1)
         for (uint32_t h = 0; h < heads; h++) {
             for (uint32_t j = 0; j < padded; j++)
@@ -498,6 +504,16 @@ void h3o_sdpa_bf16_rows(uint16_t *out, const uint16_t *q, const uint16_t *k,
 #pragma omp simd
                     for (uint32_t j = 0; j < padded; j++)
                         scores[j] = fmaf(qd, krow[j], scores[j]);
+                }
+                if (sparse_ptr) {
+                    /* keep the scores of the listed tiles, everything else becomes -inf */
+                    uint32_t qb = i / 128u;
+                    for (uint32_t j = 0; j < seq; j++) keep[j] = 0;
+                    for (uint32_t e = sparse_ptr[qb]; e < sparse_ptr[qb + 1]; e++)
+                        for (uint32_t j = sparse_idx[e] * 64u; j < sparse_idx[e] * 64u + 64u && j < seq; j++)
+                            keep[j] = 1;
+                    for (uint32_t j = 0; j < seq; j++)
+                        if (!keep[j]) scores[j] = -INFINITY;
                 }
                 float mx = -INFINITY;
                 for (uint32_t j = 0; j < seq; j++) {
@@ -530,7 +546,24 @@ void h3o_sdpa_bf16_rows(uint16_t *out, const uint16_t *q, const uint16_t *k,
         free(vf);
         free(scores);
         free(acc);
+        free(keep);
     }
+}
+
+void h3o_sdpa_bf16_rows(uint16_t *out, const uint16_t *q, const uint16_t *k,
+                        const uint16_t *v, uint32_t seq, uint32_t heads,
+                        uint32_t hd, float scale, int head_major, int round_p,
+                        uint32_t row_begin, uint32_t row_end) {
+    sdpa_core(out, q, k, v, seq, heads, hd, scale, head_major, round_p, row_begin, row_end,
+              NULL, NULL);
+}
+
+void h3o_sdpa_bf16_sparse(uint16_t *out, const uint16_t *q, const uint16_t *k,
+                          const uint16_t *v, uint32_t seq, uint32_t heads,
+                          uint32_t hd, float scale, int head_major, int round_p,
+                          const uint32_t *sparse_ptr, const uint32_t *sparse_idx) {
+    sdpa_core(out, q, k, v, seq, heads, hd, scale, head_major, round_p, 0, seq, sparse_ptr,
+              sparse_idx);
 }
 
 void h3o_sdpa_bf16(uint16_t *out, const uint16_t *q, const uint16_t *k,

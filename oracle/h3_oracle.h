@@ -139,6 +139,12 @@ void h3o_sdpa_bf16_rows(uint16_t *out, const uint16_t *q, const uint16_t *k,
 
 /* h3_cuda_core.cu:374-403: F32 rows x F32 weight + bias -> BF16, written at
  * (row_map ? row_map[r] : offset_rows + r). */
+/* attention under a block-sparse mask: CSR over 64-key tiles per 128-row query block, the form
+ * h3_gpu_sdpa_set_sparse takes (h3_gpu.h:44-51, h3_cuda_attention.cu:1652-1673) */
+void h3o_sdpa_bf16_sparse(uint16_t *out, const uint16_t *q, const uint16_t *k,
+                          const uint16_t *v, uint32_t seq, uint32_t heads,
+                          uint32_t hd, float scale, int head_major, int round_p,
+                          const uint32_t *sparse_ptr, const uint32_t *sparse_idx);
 void h3o_patch_linear_bf16(uint16_t *out, const float *in, const float *weight,
                            const float *bias, const uint32_t *row_map,
                            uint32_t offset_rows, uint32_t rows,

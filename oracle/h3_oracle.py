@@ -209,6 +209,15 @@ def sdpa_bf16(q, k, v, seq, heads, hd, scale, head_major=0, round_p=0, rows=None
     return out
 
 
+def sdpa_bf16_sparse(q, k, v, seq, heads, hd, scale, sparse_ptr, sparse_idx, head_major=0, round_p=0):
+    out = np.empty(seq * heads * hd, np.uint16)
+    ptr = np.ascontiguousarray(sparse_ptr, np.uint32)
+    idx = np.ascontiguousarray(sparse_idx, np.uint32)
+    lib().h3o_sdpa_bf16_sparse(_p(out), _p(q), _p(k), _p(v), u32(seq), u32(heads), u32(hd),
+                               f32(scale), C.c_int(head_major), C.c_int(round_p), _p(ptr), _p(idx))
+    return out
+
+
 def patch_linear_bf16(out, x, weight, bias, row_map, offset_rows, rows, in_dim, out_dim):
     lib().h3o_patch_linear_bf16(_p(out), _p(x), _p(weight), _p(bias), _p(row_map),
                                 u32(offset_rows), u32(rows), u32(in_dim), u32(out_dim))

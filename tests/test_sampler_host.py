@@ -127,3 +127,23 @@ def test_cfg_combine_oracle_formula():
     want = uf + 3.0 * (cf - uf)
     assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -8 + 1e-30)
     assert np.array_equal(o.cfg_combine_bf16(c, u, 1.0), c)     # guidance 1 returns cond exactly
+
+
+def test_oracle_masked_attention_reduces_to_dense_cases():
+    """The CPU oracle's block-sparse attention: a mask listing every tile is the dense result,
+    and a block restricted to one 64-key tile equals dense attention over those 64 keys."""
+    import h3_oracle as o
+    rng = np.random.default_rng(0)
+    S, H = 200, 2
+    q, k, v = [o.to_bf16(rng.standard_normal(S * H * 128, dtype=np.float32)) for _ in range(3)]
+    qb, kt = (S + 127) // 128, (S + 63) // 64
+    ptr = np.arange(qb + 1, dtype=np.uint32) * kt
+    idx = np.tile(np.arange(kt, dtype=np.uint32), qb)
+    dense = o.sdpa_bf16(q, k, v, S, H, 128, 0.088, round_p=1)
+    assert np.array_equal(o.sdpa_bf16_sparse(q, k, v, S, H, 128, 0.088, ptr, idx, round_p=1), dense)
+    ptr = np.array([0, 1, 1 + kt], np.uint32)
+    idx = np.concatenate([[0], np.arange(kt)]).astype(np.uint32)
+    got = o.sdpa_bf16_sparse(q, k, v, S, H, 128, 0.088, ptr, idx, round_p=1).reshape(S, H, 128)
+    first = [a.reshape(S, H, 128)[:64].reshape(-1) for a in (q, k, v)]
+    small = o.sdpa_bf16(*first, 64, H, 128, 0.088, round_p=1).reshape(64, H, 128)
+    assert np.array_equal(got[:64], small)
