@@ -112,6 +112,74 @@ def cpu_sample(shape, sequence, gemm_rows=256, attn_rows=128):
     return block_s * s.blocks * 1e3, desc, o.threads(), t_rows + t_attn
 
 
+REF_CUDA = ROOT / "oracle" / "_ref" / "libh3ref.so"
+
+
+def reference_cuda_block(shape, sequence, text_rows, repeats=3):
+    """One DiT block at the workload's S through the reference's own CUDA backend (its sources
+    compiled as a checker under oracle/_ref: cuBLASLt GEMMs, mma.sync attention, unfused row
+    kernels), driven by the same host sequence: the kernel path to beat on the same GPU.
+    Returns None when the library or a GPU is absent."""
+    try:
+        import torch
+        if not (REF_CUDA.exists() and torch.cuda.is_available()):
+            return None
+        import __graft_entry__ as entry
+        pkg = entry.load_package()
+        gpu = pkg.Gpu(0, lib_path=REF_CUDA)
+    except Exception as err:                       # the supplementary figure must not sink the arm
+        return {"unavailable": str(err)[:200]}
+    try:
+        s = shape
+        rng = np.random.default_rng(0)
+
+        def normal(n, std):
+            out = np.empty(n, np.uint16)
+            for i in range(0, n, 1 << 24):
+                m = min(1 << 24, n - i)
+                f = (rng.standard_normal(m, dtype=np.float32) * np.float32(std)).view(np.uint32)
+                out[i:i + m] = ((f + 0x7fff + ((f >> 16) & 1)) >> 16).astype(np.uint16)
+            return out
+        one = np.uint16(0x3f80)
+        t = {}
+        for name, count in pkg.block_tensor_shapes(s, 6).items():
+            if name in ("norm1", "norm2", "q_norm", "k_norm"):
+                t[name] = gpu.bf16(np.full(count, one, np.uint16))
+            else:
+                t[name] = gpu.bf16(normal(count, 0.13 if name == "modulation" else 0.02))
+        w = pkg.BlockWeights(**t)
+        dit = pkg.Dit(gpu, s, sequence)
+        dit.hidden.write(normal(sequence * s.hidden, 1.0))
+        row_map = gpu.u32(np.concatenate([np.full(text_rows, 4, np.uint32),
+                                          np.full(sequence - text_rows, 3, np.uint32)]))
+        pos = pkg.grid_positions(text_rows, max(1, -(-(sequence - text_rows) // 1024)), 32, 32)[:sequence]
+        ang = pos[:, :, None] * pkg.default_inv_freq()[None, None, :]
+        tables = []
+        for fn in (np.cos, np.sin):
+            f = fn(ang).reshape(-1).astype(np.float32).view(np.uint32)
+            tables.append(gpu.bf16(((f + 0x7fff + ((f >> 16) & 1)) >> 16).astype(np.uint16)))
+        import torch
+        for _ in range(2):
+            gpu.begin(); dit.run_block(w, row_map, tables[0], tables[1], False, None); gpu.submit()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gpu.begin()
+        a.record()
+        for _ in range(repeats):
+            dit.run_block(w, row_map, tables[0], tables[1], False, None)
+        b.record()
+        gpu.submit()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / repeats
+        return {"ms_per_block": ms, "ms_per_step_extrapolated": ms * s.blocks,
+                "tflops": s.block_flops(sequence) / (ms * 1e-3) / 1e12,
+                "what": "one block through oracle/_ref/libh3ref.so (the reference's CUDA backend, sm_100 build), "
+                        f"CUDA events, mean of {repeats}; step = block x {s.blocks}"}
+    except Exception as err:
+        return {"unavailable": str(err)[:200]}
+    finally:
+        gpu.close()
+
+
 def run_reference_arm(args, shape, sequence):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -133,6 +201,8 @@ def run_reference_arm(args, shape, sequence):
                          "this is the oracle port of its CPU test references, OpenMP over rows/heads"},
         "e2e": {"value": value, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if sequence <= 8192:      # supplementary: the reference's GPU path on this box (value stays the CPU arm)
+        line["reference_cuda_backend"] = reference_cuda_block(shape, sequence, WORKLOADS[args.workload][0])
     print(json.dumps(line), flush=True)
 
 
