@@ -501,10 +501,17 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     /* P_t arrives in two parts: each softmax warp publishes the first 32 of its
                      * 64 keys while it still works on the rest, so the first half of O_t += P_t.V_j
                      * (16-key groups 0,1 and 4,5) overlaps the second half of the exponentials */
-                    alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t, j & 1, stop));
-                    if (alive && t == 0)
-                        alive = __all_sync(0xffffffffu, mbar_wait(v_full + 8 * vs, vp, stop));
+                    /* Waits that are normally satisfied long before (the next K tile, this V tile)
+                     * come first: a wait in the middle of a run of MMAs lets the short queue of
+                     * the tensor pipe run dry, even when the barrier has already flipped. */
+                    if (t == 0) {
+                        alive = mbar_wait(v_full + 8 * vs, vp, stop);
+                        if (alive && more) alive = mbar_wait(k_full + 8 * ks, kp, stop);
+                    }
+                    alive = __all_sync(0xffffffffu, alive && mbar_wait(p_full + 16 * t, j & 1, stop));
                     if (!alive) break;
+                    /* the second part of P_t is usually complete by now: one fence, eight MMAs */
+                    const bool late_ready = __all_sync(0xffffffffu, mbar_try(p_full + 16 * t + 8, j & 1));
                     AT_TRACE(0, j, 1 + 2 * t);
                     tc_fence_after();
                     /* O_t += P_t . V_j : A = P_t in TMEM (first 64 columns of S_t), 8 columns and
@@ -516,9 +523,11 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     umma_ts<true>(d, a + 1 * 8, v_lo + 1 * (2048 >> 4), idesc_pv, leader);
                     umma_ts<true>(d, a + 4 * 8, v_lo + 4 * (2048 >> 4), idesc_pv, leader);
                     umma_ts<true>(d, a + 5 * 8, v_lo + 5 * (2048 >> 4), idesc_pv, leader);
-                    alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t + 8, j & 1, stop));
-                    if (!alive) break;
-                    tc_fence_after();
+                    if (!late_ready) {
+                        alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t + 8, j & 1, stop));
+                        if (!alive) break;
+                        tc_fence_after();
+                    }
                     umma_ts<true>(d, a + 2 * 8, v_lo + 2 * (2048 >> 4), idesc_pv, leader);
                     umma_ts<true>(d, a + 3 * 8, v_lo + 3 * (2048 >> 4), idesc_pv, leader);
                     umma_ts<true>(d, a + 6 * 8, v_lo + 6 * (2048 >> 4), idesc_pv, leader);
@@ -527,11 +536,6 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     if (more) {
                         /* the next scores of this tile go straight behind: in-order execution keeps
                          * them from overwriting P_t before P_t.V_j has read it */
-                        if (t == 0) {
-                            alive = __all_sync(0xffffffffu, mbar_wait(k_full + 8 * ks, kp, stop));
-                            if (!alive) break;
-                            tc_fence_after();
-                        }
                         issue_qk(t, k_lo_next);
                         if (t == AT_TILES - 1) umma_commit_if(k_empty + 8 * ks, leader);
                     }
