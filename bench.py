@@ -49,7 +49,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel, from the
 # ncu capture summarised in profiles/h3b_gemm_tc_dram_traffic_c3.md; (workload, ranks) -> bytes
-NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 841.0e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 885.8e6}
 
 
 def measured_peaks():
