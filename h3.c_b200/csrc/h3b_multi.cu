@@ -55,7 +55,7 @@ int permute(h3_gpu *gpu, h3_gpu_tensor *dst, const h3_gpu_tensor *src, uint32_t 
 /* Flag words of one rank: [0, 8) = epoch last announced by rank r, [8] = this rank's own
  * barrier count. One warp; lane r talks to rank r. */
 __global__ void h3b_peer_barrier(uint32_t *mine, h3x_ulysses_peers peers, int *status,
-                                 long long budget) {
+                                 long long cycle_limit) {
     __shared__ uint32_t epoch_shared;
     if (threadIdx.x == 0) {
         epoch_shared = mine[8] + 1;
@@ -73,7 +73,7 @@ __global__ void h3b_peer_barrier(uint32_t *mine, h3x_ulysses_peers peers, int *s
             uint32_t seen;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
             if (int32_t(seen - epoch) >= 0) break;
-            if (clock64() - start > budget) {
+            if (clock64() - start > cycle_limit) {
                 atomicExch(status, H3B_STATUS_PEER_TIMEOUT);
                 break;
             }

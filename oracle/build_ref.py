@@ -31,7 +31,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent
-REF = Path(os.environ.get("H3_REFERENCE_DIR", "/root/reference"))
+# the reference tree: H3_REFERENCE_DIR, else a directory named "reference" beside the repository
+REF = Path(os.environ.get("H3_REFERENCE_DIR", REPO.parent / "reference"))
 OUT = HERE / "_ref"
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 

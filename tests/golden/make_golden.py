@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Generate tests/golden/ref_cpu_vectors.npz from the reference's OWN CPU code.
 
-Run in a container where the reference tree is mounted (default /root/reference):
+Run where the reference tree is available (H3_REFERENCE_DIR, default: a directory named
+"reference" beside the repository):
 
     python oracle/build_ref.py --no-cuda      # compiles the reference's test references in place
     python tests/golden/make_golden.py

@@ -4,13 +4,14 @@ API (so a full libh3 links), and fails loudly - not silently - when no device is
 import ctypes as C
 import re
 import subprocess
+import os
 from pathlib import Path
 
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 LIB = ROOT / "h3.c_b200" / "libh3b200.so"
-REFERENCE_HEADER = Path("/root/reference/h3_gpu.h")
+REFERENCE_HEADER = Path(os.environ.get("H3_REFERENCE_DIR", ROOT.parent / "reference")) / "h3_gpu.h"
 
 
 @pytest.fixture(scope="module")
