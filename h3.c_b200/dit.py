@@ -250,10 +250,11 @@ class DenoiseStep:
                  self.final_row_map, self.final_weight, self.final_bias, self.video_rows, s.hidden,
                  s.video_patch, s.final_slots, 0, 1, s.eps)
 
-    def euler(self, delta: float) -> None:
+    def euler(self, delta: float, ratio: float = 0.0, previous: Tensor | None = None) -> None:
+        """sample += delta * (last + ratio * (last - previous)) (h3_gpu_euler_bf16)."""
         if self.video_rows:
-            self.dit.gpu.op("euler_bf16", self.latent, 0, self.velocity, self.velocity,
-                            self.video_rows * self.dit.s.video_patch, delta, 0.0)
+            self.dit.gpu.op("euler_bf16", self.latent, 0, self.velocity, previous or self.velocity,
+                            self.video_rows * self.dit.s.video_patch, delta, ratio)
 
 
 def serving_sigmas(evaluations: int, shift: float = 12.0) -> np.ndarray:
@@ -265,6 +266,27 @@ def serving_sigmas(evaluations: int, shift: float = 12.0) -> np.ndarray:
         base = f(1.0) - f(i) / f(evaluations)
         out[i] = f(shift) * base / (f(1.0) + (f(shift) - f(1.0)) * base)
     return out
+
+
+def reuse_schedule(steps: int, reuse_interval: int) -> list[int]:
+    """Which steps evaluate the model (h3_dit_reuse_schedule, h3_dit.c:2672-2688): the first,
+    the last and every reuse_interval-th; the others reuse an extrapolated velocity."""
+    if steps < 1 or not 1 <= reuse_interval <= 32:
+        raise ValueError("steps >= 1 and 1 <= reuse_interval <= 32")
+    return [int(reuse_interval == 1 or i == 0 or i == steps - 1 or i % reuse_interval == 0)
+            for i in range(steps)]
+
+
+def extrapolation_ratio(current_sigma: float, last_sigma: float, previous_sigma: float,
+                        have_previous: bool) -> float:
+    """Linear extrapolation weight of the velocity in sigma, clamped to [-2, 2]
+    (h3_dit.c:2644-2655), in F32 arithmetic like the reference."""
+    if not have_previous:
+        return 0.0
+    f = np.float32
+    denominator = f(last_sigma) - f(previous_sigma)
+    ratio = (f(current_sigma) - f(last_sigma)) / denominator if denominator != 0 else f(0.0)
+    return float(min(f(2.0), max(f(-2.0), ratio)))
 
 
 class EulerSampler:
@@ -280,8 +302,14 @@ class EulerSampler:
 
     def __init__(self, step: DenoiseStep, sigmas: np.ndarray, row_maps: list[Tensor],
                  final_row_maps: list[Tensor], *, guidance: float | None = None,
-                 uncond_text: Tensor | None = None, pair=None):
+                 uncond_text: Tensor | None = None, pair=None, reuse_interval: int = 1):
         self.step, self.sigmas = step, np.asarray(sigmas, np.float32)
+        self.selected = reuse_schedule(len(self.sigmas) - 1, reuse_interval)
+        self.reuse_interval = reuse_interval
+        self.previous_velocity = None
+        if reuse_interval > 1:
+            self.previous_velocity = step.dit.gpu.new(
+                max(1, step.video_rows) * step.dit.s.video_patch, BF16)
         self.row_maps, self.final_row_maps = row_maps, final_row_maps
         self.guidance, self.uncond_text, self.pair = guidance, uncond_text, pair
         if guidance is not None and (uncond_text is None) == (pair is None):
@@ -311,13 +339,28 @@ class EulerSampler:
             g.op("h3x_cfg_combine_bf16", st.velocity, cond, uncond, n, float(self.guidance))
 
     def run(self) -> None:
-        g = self.step.dit.gpu
-        steps = len(self.sigmas) - 1
+        """With reuse_interval > 1 only the selected steps evaluate the model; the others apply
+        the last velocity extrapolated linearly in sigma from the last two evaluations
+        (h3_dit.c:2805-2863)."""
+        st, g, sig = self.step, self.step.dit.gpu, self.sigmas
+        steps = len(sig) - 1
+        n = st.video_rows * st.dit.s.video_patch
+        last, previous = -1, -1
         g.begin()
         for i in range(steps):
-            self._velocity(i)
-            self.step.euler(float(self.sigmas[i] - self.sigmas[i + 1]))
-            if i + 1 < steps:
+            evaluate = self.selected[i]
+            if evaluate:
+                if last >= 0 and self.reuse_interval > 1:
+                    if n:
+                        g.op("copy_bf16", self.previous_velocity, 0, st.velocity, 0, n)
+                    previous = last
+                self._velocity(i)
+                last = i
+            ratio = 0.0 if evaluate else extrapolation_ratio(
+                sig[i], sig[last], sig[previous] if previous >= 0 else 0.0, previous >= 0)
+            st.euler(float(sig[i] - sig[i + 1]), ratio,
+                     self.previous_velocity if previous >= 0 else None)
+            if evaluate and i + 1 < steps:
                 g.flush()
         g.submit()
 

@@ -111,20 +111,33 @@ def oracle_velocity(c: DenoiseCase, latent, text, step):
     return velocity
 
 
-def oracle_denoise(c: DenoiseCase, guidance=None):
+def oracle_denoise(c: DenoiseCase, guidance=None, selected=None, ratio_of=None):
+    """selected[i] = 0 skips the model at step i and applies the last velocity extrapolated from
+    the last two evaluations with weight ratio_of(current, last, previous, have_previous), as the
+    reference's reuse schedule does (h3_dit.c:2805-2863)."""
     latent = c.latent.copy()
+    v = prev_v = None
+    last = previous = -1
     for i in range(c.steps):
-        v = oracle_velocity(c, latent, c.text, i)
-        if guidance is not None:
-            v = o.cfg_combine_bf16(v, oracle_velocity(c, latent, c.text_uncond, i), guidance)
-        latent = o.euler_bf16(latent, v, v, float(c.sigmas[i] - c.sigmas[i + 1]), 0.0)
+        evaluate = selected is None or selected[i]
+        if evaluate:
+            if last >= 0 and selected is not None:
+                prev_v, previous = v, last
+            v = oracle_velocity(c, latent, c.text, i)
+            if guidance is not None:
+                v = o.cfg_combine_bf16(v, oracle_velocity(c, latent, c.text_uncond, i), guidance)
+            last = i
+        ratio = 0.0 if evaluate else ratio_of(c.sigmas[i], c.sigmas[last],
+                                              c.sigmas[previous] if previous >= 0 else 0.0, previous >= 0)
+        latent = o.euler_bf16(latent, v, prev_v if previous >= 0 else v,
+                              float(c.sigmas[i] - c.sigmas[i + 1]), ratio)
     return latent
 
 
 # ------------------------------------------------------------------ library
 
 def gpu_denoise(pkg, gpu, c: DenoiseCase, *, guidance=None, exchange=None, pair=None, text=None,
-                alloc=None):
+                alloc=None, reuse_interval=1):
     """Runs the whole loop on `gpu`; with an exchange, on this rank's row slice. Returns the
     F32 latent rows this rank owns (video rows only)."""
     shape = pkg.DitShape(hidden=c.hidden_dim, heads=c.heads, ffn=c.ffn, blocks=len(c.blocks))
@@ -158,7 +171,7 @@ def gpu_denoise(pkg, gpu, c: DenoiseCase, *, guidance=None, exchange=None, pair=
     if guidance is not None and pair is None:
         uncond = gpu.bf16(rows_of(c.text_uncond, c.hidden_dim, np.uint16, r0, local_text, local_text))
     sampler = pkg.EulerSampler(step, c.sigmas, row_maps, final_maps, guidance=guidance,
-                               uncond_text=uncond, pair=pair)
+                               uncond_text=uncond, pair=pair, reuse_interval=reuse_interval)
     sampler.run()
     return step.latent.read()[:local_video * PATCH], (video_begin, local_video)
 

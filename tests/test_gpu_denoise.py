@@ -45,6 +45,21 @@ def test_small_denoise_matches_oracle(pkg, guidance):
     assert rel_l2(want, case.latent) > 0.05      # the loop moved the latent: the check is not vacuous
 
 
+def test_reuse_schedule_denoise_matches_oracle(pkg):
+    """7 steps with reuse interval 3: steps 0, 3, 6 evaluate the model, the others extrapolate."""
+    case = make_denoise_case(rows=200, text_rows=40, blocks=2, steps=7, seed=5,
+                             sigmas=pkg.serving_sigmas(7))
+    want = oracle_denoise(case, selected=pkg.reuse_schedule(7, 3), ratio_of=pkg.extrapolation_ratio)
+    gpu = pkg.Gpu(0)
+    try:
+        got, _ = gpu_denoise(pkg, gpu, case, reuse_interval=3)
+    finally:
+        gpu.close()
+    cos, r = cosine(got, want), rel_l2(got, want)
+    print(f"7-step denoise, reuse interval 3: cosine={cos:.7f} rel_l2={r:.3e}")
+    assert cos >= 0.999 and r <= 1e-2
+
+
 @pytest.mark.skipif(not REF_CUDA.exists(), reason="reference CUDA backend was not built")
 def test_full_width_denoise_matches_reference_cuda_backend(pkg):
     """4 blocks x 4 Euler steps at hidden 5376 / 56 heads / FFN 14336, S = 1,664 (config-1 rows)."""

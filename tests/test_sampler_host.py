@@ -24,6 +24,26 @@ def test_serving_sigmas_known_answers(pkg):
     assert np.all(np.diff(a4) < 0)
 
 
+def test_reuse_schedule_known_answers(pkg):
+    """tests/test_h3.c:128-147 of the reference."""
+    sel = pkg.reuse_schedule(20, 3)
+    assert sum(sel) == 8 and [i for i, v in enumerate(sel) if v] == [0, 3, 6, 9, 12, 15, 18, 19]
+    sel = pkg.reuse_schedule(20, 2)
+    assert sum(sel) == 11 and all(v == (i % 2 == 0 or i == 19) for i, v in enumerate(sel))
+    sel = pkg.reuse_schedule(50, 3)
+    assert sum(sel) == 18 and all(v == (i % 3 == 0 or i == 49) for i, v in enumerate(sel))
+    assert sum(pkg.reuse_schedule(20, 1)) == 20
+    with pytest.raises(ValueError):
+        pkg.reuse_schedule(20, 33)
+
+
+def test_extrapolation_ratio(pkg):
+    assert pkg.extrapolation_ratio(0.5, 0.6, 0.7, False) == 0.0
+    assert abs(pkg.extrapolation_ratio(0.5, 0.6, 0.7, True) - 1.0) < 1e-6      # one interval further
+    assert pkg.extrapolation_ratio(0.0, 0.6, 0.7, True) == 2.0                  # clamped
+    assert pkg.extrapolation_ratio(0.5, 0.6, 0.6, True) == 0.0                  # degenerate schedule
+
+
 class FakeTensor:
     def __init__(self, name):
         self.name = name
@@ -65,8 +85,11 @@ class FakeStep:
     def forward(self):
         self.dit.gpu.log.append(("forward", self.text_hidden.name, self.row_map.name, self.final_row_map.name))
 
-    def euler(self, delta):
-        self.dit.gpu.log.append(("euler", round(delta, 6)))
+    def euler(self, delta, ratio=0.0, previous=None):
+        entry = ("euler", round(delta, 6))
+        if ratio or previous is not None:
+            entry += (round(ratio, 6), previous.name if previous is not None else None)
+        self.dit.gpu.log.append(entry)
 
 
 def maps(n):
@@ -80,6 +103,21 @@ def test_plain_loop(pkg):
     pkg.EulerSampler(step, sig, *maps(2)).run()
     assert gpu.log == ["begin", ("forward", "cond_text", "rm0", "frm0"), ("euler", 0.5), "flush",
                        ("forward", "cond_text", "rm1", "frm1"), ("euler", 0.5), "submit"]
+
+
+def test_reuse_loop(pkg):
+    """5 steps, interval 2: steps 0, 2, 4 evaluate; 1 reuses the only velocity, 3 extrapolates."""
+    gpu = FakeGpu()
+    step = FakeStep(gpu, pkg)
+    sig = np.array([1.0, 0.8, 0.6, 0.4, 0.2, 0.0], np.float32)
+    pkg.EulerSampler(step, sig, *maps(5), reuse_interval=2).run()
+    f = lambda i: ("forward", "cond_text", f"rm{i}", f"frm{i}")
+    keep = ("copy_bf16", "new960", 0, "velocity", 0, 960)
+    assert gpu.log == ["begin", f(0), ("euler", 0.2), "flush",
+                       ("euler", 0.2),
+                       keep, f(2), ("euler", 0.2, 0.0, "new960"), "flush",
+                       ("euler", 0.2, 0.5, "new960"),
+                       keep, f(4), ("euler", 0.2, 0.0, "new960"), "submit"]
 
 
 def test_sequential_guidance(pkg):
