@@ -265,11 +265,10 @@ constexpr int AT_TILES = 2;             /* query tiles per CTA           */
 constexpr int AT_Q = AT_QT * AT_TILES;  /* query rows per CTA            */
 constexpr int AT_KV = 128;              /* keys per tile                 */
 constexpr int AT_D = 128;               /* head dim                      */
-constexpr bool AT_POLY_EXP2 = true;   /* one score in four takes the polynomial exp2 */
 constexpr int AT_K_STAGES = 3;
 constexpr int AT_V_STAGES = 2;
 constexpr int AT_SOFTMAX_WARPS = 8 * AT_TILES;   /* per tile: 4 lane quarters x 2 key halves */
-constexpr int AT_THREADS = 128 + 32 * AT_SOFTMAX_WARPS;  /* warpgroup 0: producer, MMA, two idle warps; then the softmax warps */
+constexpr int AT_THREADS = 64 + 32 * AT_SOFTMAX_WARPS;  /* producer, MMA, softmax warps */
 constexpr int AT_Q_BYTES = AT_Q * AT_D * 2;      /* 64 KiB: two boxes of [256 rows][64 dims] */
 constexpr int AT_K_BYTES = AT_KV * AT_D * 2;     /* 32 KiB: two boxes of [128 keys][64 dims] */
 constexpr int AT_V_BYTES = AT_KV * AT_D * 2;     /* 32 KiB: two boxes                        */
@@ -367,20 +366,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-/* 2^x on the FMA pipe instead of the MUFU: x = n + r by a magic-number add (round to nearest),
- * degree-3 minimax polynomial of 2^r on [-0.5, 0.5] (max relative error 7.5e-5, far below the
- * 2^-9 of the BF16 rounding that follows), exponent added in the integer domain. x is clamped
- * at -126 (a masked score gives ~1e-38 instead of 0). All constants are immediates. */
-__device__ __forceinline__ float exp2_poly(float x) {
-    x = fmaxf(x, -126.0f);
-    const float u = x + 12582912.0f;
-    const float r = x - (u - 12582912.0f);
-    float p = fmaf(0.0551716685f, r, 0.2426111251f);
-    p = fmaf(p, r, 0.6932609677f);
-    p = fmaf(p, r, 0.9999280572f);
-    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(u) << 23));
-}
-
 /* V tile [128 keys][128 dims] is held as two boxes of [128 keys][64 dims] with 128-byte
  * swizzle and read as an N-major B operand: along N, 64-element groups are one box
  * (16384 bytes) apart = leading byte offset; along K, groups of 8 keys are 1024 bytes
@@ -451,11 +436,6 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
 
-    /* Register budget by warpgroup: the producer / MMA warpgroup gives most of its registers to
-     * the four softmax warpgroups (one per (query tile, key half), its four warps = the four
-     * tensor-memory lane quarters). 128 x 32 + 512 x 112 = 640 x 96 registers. */
-    if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
     if (warp == 0) {
         /* ------------------------------------------------ TMA producer */
         if (lane == 0) {
@@ -567,15 +547,13 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
             }
             if (alive) umma_commit_if(o_done, leader);
         }
-    }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;" ::: "memory");
         /* ------------------------------------------------------ softmax */
         /* 16 warps: query tile (2) x key half (2) x lane quarter (4). A thread owns one query
          * row (its TMEM lane) and 64 of the 128 keys of a tile; the two warps that share a
          * row exchange their maxima through shared memory, so both use the same reference
          * maximum, and keep separate partial row sums that are added at the end. */
-        const uint32_t idx = uint32_t(warp - 4);
+        const uint32_t idx = uint32_t(warp - 2);
         const uint32_t tile = idx >> 3, half = (idx >> 2) & 1u;
         const uint32_t quarter = warp & 3;
         const uint32_t local_row = quarter * 32 + lane;
@@ -693,8 +671,7 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     unpack_f32x2(xa, x0, x1);
                     unpack_f32x2(xb, x2, x3);
                     const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                    const float p2 = fast_exp2(x2);
-                    const float p3 = AT_POLY_EXP2 ? exp2_poly(x3) : fast_exp2(x3);
+                    const float p2 = fast_exp2(x2), p3 = fast_exp2(x3);
                     sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
                     sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
                     packed[2 * i] = pack_bf16(p0, p1);
