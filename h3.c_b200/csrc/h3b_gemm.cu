@@ -163,6 +163,89 @@ __device__ __forceinline__ void qkv_unit_epilogue(const TcArgs &args, uint32_t l
     __syncwarp();
 }
 
+/* One thread's share of a finished 128 x 256 accumulator tile: its row (TMEM lane) through the
+ * epilogue EPI. lane_addr = TMEM address of the row's first column. */
+template <int EPI>
+__device__ __forceinline__ void tile_epilogue(const TcArgs &args, uint32_t lane_addr, uint32_t row,
+                                              bool row_ok, uint32_t n_blk, uint32_t stage_smem,
+                                              uint32_t lane) {
+                if (EPI == H3B_EPI_QKV_ROPE) {
+                    /* the tile's 256 columns are two whole 128-column units of the grouped row */
+    #pragma unroll 1
+                    for (uint32_t u = 0; u < 2; u++) {
+                        const uint32_t unit = n_blk * 2 + u;
+                        if (unit < args.heads * 3)
+                            qkv_unit_epilogue(args, lane_addr + u * 128, unit, row, row_ok,
+                                              stage_smem, lane);
+                    }
+                } else if (EPI == H3B_EPI_SWIGLU) {
+                    uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * 128;
+    #pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t g[32], u[32];
+                        tmem_ld32(lane_addr + c * 32, g);
+                        tmem_ld32(lane_addr + 128 + c * 32, u);
+                        tmem_ld_wait();
+                        uint32_t col0 = n_blk * 128 + c * 32;
+                        uint32_t packed[16];
+    #pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            float g0 = round_bf16(__uint_as_float(g[2 * i]));
+                            float g1 = round_bf16(__uint_as_float(g[2 * i + 1]));
+                            float u0 = round_bf16(__uint_as_float(u[2 * i]));
+                            float u1 = round_bf16(__uint_as_float(u[2 * i + 1]));
+                            packed[i] = pack_bf16(g0 / (1.0f + expf(-g0)) * u0,
+                                                   g1 / (1.0f + expf(-g1)) * u1);
+                        }
+                        if (row_ok) {
+    #pragma unroll
+                            for (int v = 0; v < 4; v++)
+                                if (col0 + v * 8 < args.out_cols)
+                                    *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = make_uint4(
+                                        packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
+                                        packed[4 * v + 3]);
+                        }
+                    }
+                } else {
+                    uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * BN;
+    #pragma unroll 1
+                    for (int c = 0; c < BN / 32; c++) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_addr + c * 32, r);
+                        tmem_ld_wait();
+                        uint32_t col0 = n_blk * BN + c * 32;
+                        uint32_t packed[16];
+                        if (args.bias) {
+    #pragma unroll
+                            for (int v = 0; v < 4; v++) {
+                                uint4 b = make_uint4(0, 0, 0, 0);
+                                if (col0 + v * 8 < args.out_cols)
+                                    b = __ldg(reinterpret_cast<const uint4 *>(args.bias + col0 + v * 8));
+                                const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+    #pragma unroll
+                                for (int i = 0; i < 4; i++)
+                                    packed[4 * v + i] = pack_bf16(
+                                        __uint_as_float(r[8 * v + 2 * i]) + h3b_lo(bw[i]),
+                                        __uint_as_float(r[8 * v + 2 * i + 1]) + h3b_hi(bw[i]));
+                            }
+                        } else {
+    #pragma unroll
+                            for (int i = 0; i < 16; i++)
+                                packed[i] = pack_bf16(__uint_as_float(r[2 * i]),
+                                                       __uint_as_float(r[2 * i + 1]));
+                        }
+                        if (row_ok) {
+    #pragma unroll
+                            for (int v = 0; v < 4; v++)
+                                if (col0 + v * 8 < args.out_cols)
+                                    *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = make_uint4(
+                                        packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
+                                        packed[4 * v + 3]);
+                        }
+                    }
+                }
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -289,81 +372,8 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t row = m_blk * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
             const bool row_ok = row < args.rows;
-            if (EPI == H3B_EPI_QKV_ROPE) {
-                /* the tile's 256 columns are two whole 128-column units of the grouped row */
-#pragma unroll 1
-                for (uint32_t u = 0; u < 2; u++) {
-                    const uint32_t unit = n_blk * 2 + u;
-                    if (unit < args.heads * 3)
-                        qkv_unit_epilogue(args, lane_addr + u * 128, unit, row, row_ok,
-                                          bars + 256 + quarter * QKV_STAGE_BYTES, lane);
-                }
-            } else if (EPI == H3B_EPI_SWIGLU) {
-                uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * 128;
-#pragma unroll 1
-                for (int c = 0; c < 4; c++) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(lane_addr + c * 32, g);
-                    tmem_ld32(lane_addr + 128 + c * 32, u);
-                    tmem_ld_wait();
-                    uint32_t col0 = n_blk * 128 + c * 32;
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        float g0 = round_bf16(__uint_as_float(g[2 * i]));
-                        float g1 = round_bf16(__uint_as_float(g[2 * i + 1]));
-                        float u0 = round_bf16(__uint_as_float(u[2 * i]));
-                        float u1 = round_bf16(__uint_as_float(u[2 * i + 1]));
-                        packed[i] = pack_bf16(g0 / (1.0f + expf(-g0)) * u0,
-                                               g1 / (1.0f + expf(-g1)) * u1);
-                    }
-                    if (row_ok) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            if (col0 + v * 8 < args.out_cols)
-                                *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = make_uint4(
-                                    packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
-                                    packed[4 * v + 3]);
-                    }
-                }
-            } else {
-                uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * BN;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_addr + c * 32, r);
-                    tmem_ld_wait();
-                    uint32_t col0 = n_blk * BN + c * 32;
-                    uint32_t packed[16];
-                    if (args.bias) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++) {
-                            uint4 b = make_uint4(0, 0, 0, 0);
-                            if (col0 + v * 8 < args.out_cols)
-                                b = __ldg(reinterpret_cast<const uint4 *>(args.bias + col0 + v * 8));
-                            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                            for (int i = 0; i < 4; i++)
-                                packed[4 * v + i] = pack_bf16(
-                                    __uint_as_float(r[8 * v + 2 * i]) + h3b_lo(bw[i]),
-                                    __uint_as_float(r[8 * v + 2 * i + 1]) + h3b_hi(bw[i]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; i++)
-                            packed[i] = pack_bf16(__uint_as_float(r[2 * i]),
-                                                   __uint_as_float(r[2 * i + 1]));
-                    }
-                    if (row_ok) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            if (col0 + v * 8 < args.out_cols)
-                                *reinterpret_cast<uint4 *>(dst + c * 32 + v * 8) = make_uint4(
-                                    packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
-                                    packed[4 * v + 3]);
-                    }
-                }
-            }
+            tile_epilogue<EPI>(args, lane_addr, row, row_ok, n_blk,
+                               bars + 256 + quarter * QKV_STAGE_BYTES, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
@@ -383,6 +393,171 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == 1) {
         tc_fence_after();
         tmem_free(tmem_base, 512);
+    }
+}
+
+/* ---- the same GEMM on CTA pairs ------------------------------------------------------
+ * Cluster of two CTAs = one 256 x 256 output tile: CTA r owns rows [128 r, 128 r + 128) of the
+ * tile (its own A slab and its own 128 x 256 accumulator in tensor memory) and loads only half
+ * of the weight tile (weight rows [128 r, 128 r + 128) of the 256); the even CTA issues
+ * tcgen05.mma.cta_group::2 (M = 256), which reads both halves. Per output element the pair
+ * pulls 2/3 of the operand bytes a lone CTA needs, and the weight stream, which is what limits
+ * the lone-CTA kernel on the large projections, is halved. Barriers: TMA bytes of both CTAs
+ * complete on the even CTA's full barrier; the MMA's commits arrive on the empty / accumulator
+ * barriers of both CTAs; the epilogue warps of both CTAs arrive on the even CTA's
+ * accumulator-free barrier. Every wait is bounded as in the lone-CTA kernel. */
+constexpr int PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2;          /* 32 KiB per CTA and stage */
+template <int EPI>
+constexpr int pair_stages() { return EPI == H3B_EPI_QKV_ROPE ? 5 : 6; }
+template <int EPI>
+constexpr size_t pair_smem() {
+    return size_t(pair_stages<EPI>()) * PAIR_STAGE_BYTES + 1024 + 256 +
+           (EPI == H3B_EPI_QKV_ROPE ? 4 * QKV_STAGE_BYTES : 0);
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              TcArgs args) {
+    constexpr int NS = pair_stages<EPI>();
+    extern __shared__ uint8_t raw_smem[];
+    __shared__ int stop_flag;
+    const uint32_t base = (smem_u32(raw_smem) + 1023u) & ~1023u;
+    const uint32_t a_smem = base;
+    const uint32_t b_smem = base + NS * A_BYTES;
+    const uint32_t bars = b_smem + NS * (B_BYTES / 2);
+    const uint32_t full_bar = bars;                   /* NS x 8, used in the even CTA */
+    const uint32_t empty_bar = bars + 8 * NS;         /* NS x 8, per CTA              */
+    const uint32_t acc_full = bars + 16 * NS;         /* 2 x 8, per CTA               */
+    const uint32_t acc_empty = acc_full + 16;         /* 2 x 8, used in the even CTA  */
+    const uint32_t tmem_holder = acc_empty + 16;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    volatile int *stop = &stop_flag;
+
+    if (threadIdx.x == 0) {
+        stop_flag = 0;
+        for (int s = 0; s < NS; s++) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(acc_full + 8 * i, 1);
+            mbar_init(acc_empty + 8 * i, 8);          /* 4 epilogue warps x 2 CTAs */
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_holder, 512);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          /* the peer's barriers exist before anything signals them */
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
+
+    const uint32_t total_tiles = args.tiles_m * args.tiles_n;     /* tiles_m counts 256-row tiles */
+    const uint32_t group_tiles = args.group_m * args.tiles_n;
+    auto tile_coords = [&](uint32_t tile, uint32_t &m_blk, uint32_t &n_blk) {
+        uint32_t group = tile / group_tiles, local = tile % group_tiles;
+        uint32_t first_m = group * args.group_m;
+        uint32_t group_m = min(args.tiles_m - first_m, args.group_m);
+        m_blk = first_m + local % group_m;
+        n_blk = local / group_m;
+    };
+
+    if (warp == 0) {
+        /* ---- TMA producer (both CTAs): own A rows, own half of the weight tile ---- */
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+                uint32_t m_blk, n_blk;
+                tile_coords(tile, m_blk, n_blk);
+                const int a_row = int(m_blk * 256 + rank * BM);
+                const int b_row = EPI == H3B_EPI_SWIGLU
+                                      ? int((rank ? args.up_offset : 0u) + n_blk * 128)
+                                      : int(n_blk * BN + rank * 128);
+                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop)) { alive = false; break; }
+                    const uint32_t bar = cluster_map(full_bar + 8 * stage, 0);
+                    if (rank == 0) mbar_expect_tx(full_bar + 8 * stage, 2 * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(a_smem + stage * A_BYTES, &map_a, bar, int(kb * BK), a_row);
+                    tma_load_2d_pair(b_smem + stage * (B_BYTES / 2), &map_b, bar, int(kb * BK), b_row);
+                    if (++stage == NS) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ---- MMA issuer: the even CTA only ---- */
+        if (rank == 0) {
+            const uint32_t leader = lane == 0;
+            constexpr uint32_t idesc = instruction_desc(256, BN);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
+            bool alive = true;
+            for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop))) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_lo = a_lo0 + stage * (A_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * ((B_BYTES / 2) >> 4);
+                    if (kb == 0) umma_ss_pair<false>(d_tmem, a_lo, b_lo, idesc, leader);
+                    else umma_ss_pair<true>(d_tmem, a_lo, b_lo, idesc, leader);
+#pragma unroll
+                    for (int k = 1; k < BK / 16; k++)
+                        umma_ss_pair<true>(d_tmem, a_lo + 2 * k, b_lo + 2 * k, idesc, leader);
+                    umma_commit_pair_if(empty_bar + 8 * stage, leader);
+                    if (++stage == NS) { stage = 0; phase ^= 1; }
+                }
+                if (!alive) break;
+                umma_commit_pair_if(acc_full + 8 * acc, leader);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        /* ---- epilogue (both CTAs): warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ---- */
+        const uint32_t quarter = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
+            uint32_t m_blk, n_blk;
+            tile_coords(tile, m_blk, n_blk);
+            if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop)) break;
+            tc_fence_after();
+            const uint32_t row = m_blk * 256 + rank * BM + quarter * 32 + lane;
+            const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
+            tile_epilogue<EPI>(args, lane_addr, row, row < args.rows, n_blk,
+                               bars + 256 + quarter * QKV_STAGE_BYTES, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_map(acc_empty + 8 * acc, 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*stop) {
+        if (threadIdx.x == 0) atomicMax(args.status, int(H3B_STATUS_GEMM_TIMEOUT));
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    /* neither CTA may leave (or free tensor memory) while its peer can still signal its barriers
+     * or have its shared memory read by an MMA */
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_free_pair(tmem_base, 512);
     }
 }
 
@@ -485,6 +660,38 @@ bool env_flag(const char *name) {
     return v && *v && strcmp(v, "0") != 0;
 }
 
+/* How many CTA pairs of the paired kernel the device keeps resident at once (0: clusters of two
+ * cannot be scheduled, or the kernel cannot get its shared memory); queried once per epilogue. */
+template <int EPI>
+int max_resident_pairs() {
+    static int pairs = -1;
+    if (pairs >= 0) return pairs;
+    pairs = 0;
+    if (cudaFuncSetAttribute(h3b_gemm_pair<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(pair_smem<EPI>())) != cudaSuccess) {
+        cudaGetLastError();
+        return pairs;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * 148);
+    config.blockDim = dim3(TC_THREADS);
+    config.dynamicSmemBytes = pair_smem<EPI>();
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, h3b_gemm_pair<EPI>, &config) != cudaSuccess) {
+        cudaGetLastError();
+        return pairs;
+    }
+    pairs = clusters;
+    return pairs;
+}
+
 template <int EPI>
 int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t weight_rows,
@@ -524,6 +731,22 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
         gm = gm > args.tiles_m ? args.tiles_m : gm;
         const uint32_t groups = (args.tiles_m + gm - 1) / gm;
         args.group_m = (args.tiles_m + groups - 1) / groups;
+    }
+    /* CTA pairs (256 x 256 tiles) when the problem has at least one full pair of row blocks and
+     * the device can co-schedule clusters of two */
+    const int pairs = max_resident_pairs<EPI>();
+    if (rows > BM && pairs > 0 && !env_flag("H3B_NO_CTA_PAIRS")) {
+        args.tiles_m = (rows + 2 * BM - 1) / (2 * BM);
+        const double slab = 2.0 * BM * k * 2.0;
+        uint32_t gm = uint32_t(40.0e6 / slab);
+        gm = gm < 2 ? 2 : gm;
+        gm = gm > args.tiles_m ? args.tiles_m : gm;
+        const uint32_t groups = (args.tiles_m + gm - 1) / gm;
+        args.group_m = (args.tiles_m + groups - 1) / groups;
+        const uint32_t tiles = args.tiles_m * args.tiles_n;
+        const uint32_t grid = 2 * (tiles < uint32_t(pairs) ? tiles : uint32_t(pairs));
+        h3b_gemm_pair<EPI><<<grid, TC_THREADS, pair_smem<EPI>(), gpu->stream>>>(map_a, map_b, args);
+        return 1;
     }
     uint32_t tiles = args.tiles_m * args.tiles_n;
     uint32_t grid = tiles < uint32_t(gpu->sm_count) ? tiles : uint32_t(gpu->sm_count);

@@ -197,6 +197,73 @@ __device__ __forceinline__ void umma_commit_if(uint32_t bar, uint32_t leader) {
         : "memory");
 }
 
+/* ---- CTA pairs (cluster of two, tcgen05 cta_group::2) -------------------------------------
+ * One tcgen05.mma issued by the even CTA multiplies M = 256 rows (128 from each CTA's shared
+ * memory, accumulated in each CTA's own tensor memory) by a B tile whose N rows are split
+ * between the two CTAs' shared memory. No TMA multicast is involved: each CTA loads its own
+ * halves and reports the bytes to the even CTA's mbarrier. */
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+/* shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in CTA `rank` */
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+/* TMA load into this CTA's shared memory; completion bytes go to the mbarrier at the given
+ * shared::cluster address (the even CTA's barrier) */
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map,
+                                                 uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t holder, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free_pair(uint32_t taddr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns)
+                 : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                             uint32_t idesc, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred p, l;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.u32 p, %5, 0;\n\t"
+        "setp.ne.u32 l, %6, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "@l tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(DESC_HI_SW128), "n"(ACC ? 1 : 0),
+          "r"(leader)
+        : "memory");
+}
+/* arrive on the mbarrier at the same shared-memory offset in both CTAs of the pair when all
+ * MMAs issued so far have completed */
+__device__ __forceinline__ void umma_commit_pair_if(uint32_t bar, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred l;\n\t.reg .b16 mask;\n\tsetp.ne.u32 l, %1, 0;\n\tmov.b16 mask, 3;\n\t"
+        "@l tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], mask;\n\t}"
+        ::"r"(bar), "r"(leader)
+        : "memory");
+}
+
 /* two F32 -> packed BF16x2, round to nearest even (one cvt instruction) */
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
