@@ -689,6 +689,7 @@ int max_resident_pairs() {
         return pairs;
     }
     pairs = clusters;
+    if (env_flag("H3B_REPORT_PAIRS")) fprintf(stderr, "h3b200: %d resident CTA pairs for epilogue %d\n", pairs, EPI);
     return pairs;
 }
 
@@ -732,10 +733,13 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
         const uint32_t groups = (args.tiles_m + gm - 1) / gm;
         args.group_m = (args.tiles_m + groups - 1) / groups;
     }
-    /* CTA pairs (256 x 256 tiles) when the problem has at least one full pair of row blocks and
-     * the device can co-schedule clusters of two */
+    /* CTA pairs (256 x 256 tiles) when the problem has more than one row block, the device can
+     * co-schedule clusters of two, and X is of the order of the L2 size: measured inside the
+     * power-capped step, pairs win at 6,400 rows (258 vs 265 ms per 50-block step) and lose at
+     * 50,476 rows (1,070 vs 1,024 ms per 10 blocks), where X streams from HBM as well. */
     const int pairs = max_resident_pairs<EPI>();
-    if (rows > BM && pairs > 0 && !env_flag("H3B_NO_CTA_PAIRS")) {
+    const bool pair_size = rows > BM && (rows <= 16384 || env_flag("H3B_CTA_PAIRS_ALWAYS"));
+    if (pair_size && pairs > 0 && !env_flag("H3B_NO_CTA_PAIRS")) {
         args.tiles_m = (rows + 2 * BM - 1) / (2 * BM);
         const double slab = 2.0 * BM * k * 2.0;
         uint32_t gm = uint32_t(40.0e6 / slab);
