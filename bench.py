@@ -49,7 +49,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel, from the
 # ncu capture summarised in profiles/h3b_gemm_tc_dram_traffic_c3.md; (workload, ranks) -> bytes
-NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 885.8e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 1050.3e6}
 
 
 def measured_peaks():
@@ -573,7 +573,7 @@ def run_gpu_arm(args, shape, sequence, text_rows):
                 attn_flops)
         qkv_ms, qkv_tf = kernels["qkv_proj_norm_rope"]
         roofline = {"bound": "tensor",
-                    "kernel": "h3b_gemm_tc<qkv+norm+rope> (QKV projection with fused head norm and RoPE)",
+                    "kernel": "h3b_gemm_pair<qkv+norm+rope> (QKV projection with fused head norm and RoPE, CTA pairs)",
                     "achieved": qkv_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": qkv_tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst",
                     "ms_per_launch": qkv_ms, "flops_per_launch": qkv_flops,
