@@ -573,7 +573,9 @@ def run_gpu_arm(args, shape, sequence, text_rows):
                 attn_flops)
         qkv_ms, qkv_tf = kernels["qkv_proj_norm_rope"]
         roofline = {"bound": "tensor",
-                    "kernel": "h3b_gemm_pair<qkv+norm+rope> (QKV projection with fused head norm and RoPE, CTA pairs)",
+                    "kernel": ("h3b_gemm_pair<qkv+norm+rope> (QKV projection with fused head norm and RoPE, CTA pairs)"
+                               if 128 < rows <= 16384 else
+                               "h3b_gemm_tc<qkv+norm+rope> (QKV projection with fused head norm and RoPE)"),
                     "achieved": qkv_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": qkv_tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst",
                     "ms_per_launch": qkv_ms, "flops_per_launch": qkv_flops,
