@@ -40,6 +40,7 @@ WORKLOADS = {
     "c4": (256, 50220, "864x480x121f: 50,220 video + 256 text rows (S=50,476), 50 blocks"),
     "ref512": (256, 1792 + 74, "reference-true 512x512x22f layout: 1,866 video/audio + 256 text rows"),
     "ref864": (256, 14985 + 414, "reference-true 864x480x124f layout: 15,399 video/audio + 256 text rows"),
+    "c4_quarter": (256, 12363, "a quarter of the 864x480x121f rows (S=12,619: the per-rank GEMM size of c4 on 4 GPUs), 50 blocks"),
     "c5": (256, 50220, "864x480x121f (S=50,476), 20 Euler steps with classifier-free guidance, "
                        "cond/uncond on two GPU groups, 50 blocks"),
     "c5small": (256, 6144, "512x512x22f (S=6,400), 20 Euler steps with classifier-free guidance, "
@@ -574,7 +575,7 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         qkv_ms, qkv_tf = kernels["qkv_proj_norm_rope"]
         roofline = {"bound": "tensor",
                     "kernel": ("h3b_gemm_pair<qkv+norm+rope> (QKV projection with fused head norm and RoPE, CTA pairs)"
-                               if 128 < rows <= 16384 else
+                               if 128 < rows <= 8192 else
                                "h3b_gemm_tc<qkv+norm+rope> (QKV projection with fused head norm and RoPE)"),
                     "achieved": qkv_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": qkv_tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst",

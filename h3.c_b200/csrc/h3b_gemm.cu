@@ -734,11 +734,11 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
         args.group_m = (args.tiles_m + groups - 1) / groups;
     }
     /* CTA pairs (256 x 256 tiles) when the problem has more than one row block, the device can
-     * co-schedule clusters of two, and X is of the order of the L2 size: measured inside the
-     * power-capped step, pairs win at 6,400 rows (258 vs 265 ms per 50-block step) and lose at
-     * 50,476 rows (1,070 vs 1,024 ms per 10 blocks), where X streams from HBM as well. */
+     * co-schedule clusters of two, and X fits in L2: measured inside the power-capped step, pairs
+     * win at 6,400 rows (258 vs 265 ms per 50-block step), make no difference at 12,619 rows and
+     * lose at 50,476 rows (1,070 vs 1,024 ms per 10 blocks), where X streams from HBM as well. */
     const int pairs = max_resident_pairs<EPI>();
-    const bool pair_size = rows > BM && (rows <= 16384 || env_flag("H3B_CTA_PAIRS_ALWAYS"));
+    const bool pair_size = rows > BM && (rows <= 8192 || env_flag("H3B_CTA_PAIRS_ALWAYS"));
     if (pair_size && pairs > 0 && !env_flag("H3B_NO_CTA_PAIRS")) {
         args.tiles_m = (rows + 2 * BM - 1) / (2 * BM);
         const double slab = 2.0 * BM * k * 2.0;
