@@ -40,6 +40,7 @@ WORKLOADS = {
     "c4": (256, 50220, "864x480x121f: 50,220 video + 256 text rows (S=50,476), 50 blocks"),
     "ref512": (256, 1792 + 74, "reference-true 512x512x22f layout: 1,866 video/audio + 256 text rows"),
     "ref864": (256, 14985 + 414, "reference-true 864x480x124f layout: 15,399 video/audio + 256 text rows"),
+    "c3_eighth": (256, 544, "an eighth of the 512x512x22f rows (S=800: the per-rank GEMM size of c3 on 8 GPUs), 50 blocks"),
     "c4_quarter": (256, 12363, "a quarter of the 864x480x121f rows (S=12,619: the per-rank GEMM size of c4 on 4 GPUs), 50 blocks"),
     "c5": (256, 50220, "864x480x121f (S=50,476), 20 Euler steps with classifier-free guidance, "
                        "cond/uncond on two GPU groups, 50 blocks"),

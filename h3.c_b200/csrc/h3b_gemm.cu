@@ -733,12 +733,19 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
         const uint32_t groups = (args.tiles_m + gm - 1) / gm;
         args.group_m = (args.tiles_m + groups - 1) / groups;
     }
-    /* CTA pairs (256 x 256 tiles) when the problem has more than one row block, the device can
+    /* CTA pairs (256 x 256 tiles) when that does not cost an extra round of tiles (a pair tile
+     * occupies each of its two SMs as long as a lone 128 x 256 tile; with few rows the 256-row
+     * granularity wastes more: 800 rows = 7 lone row blocks but 4 x 256), the device can
      * co-schedule clusters of two, and X fits in L2: measured inside the power-capped step, pairs
      * win at 6,400 rows (258 vs 265 ms per 50-block step), make no difference at 12,619 rows and
      * lose at 50,476 rows (1,070 vs 1,024 ms per 10 blocks), where X streams from HBM as well. */
     const int pairs = max_resident_pairs<EPI>();
-    const bool pair_size = rows > BM && (rows <= 8192 || env_flag("H3B_CTA_PAIRS_ALWAYS"));
+    bool pair_size = false;
+    if (pairs > 0 && rows > BM) {
+        const uint64_t lone_rounds = (uint64_t(args.tiles_m) * tiles_n + gpu->sm_count - 1) / gpu->sm_count;
+        const uint64_t pair_rounds = (uint64_t((rows + 2 * BM - 1) / (2 * BM)) * tiles_n + pairs - 1) / pairs;
+        pair_size = (rows <= 8192 && pair_rounds <= lone_rounds) || env_flag("H3B_CTA_PAIRS_ALWAYS");
+    }
     if (pair_size && pairs > 0 && !env_flag("H3B_NO_CTA_PAIRS")) {
         args.tiles_m = (rows + 2 * BM - 1) / (2 * BM);
         const double slab = 2.0 * BM * k * 2.0;
