@@ -458,7 +458,18 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         exchange = NcclExchange(dist, mem, world, rank)
     peaks = measured_peaks()
 
-    dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
+    try:
+        dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
+    except pkg.H3Error as err:
+        # peer mappings (CUDA IPC) are refused on this machine: every rank gets the same error
+        # and falls back to the NCCL form of the exchange
+        if not isinstance(exchange, pkg.PeerExchange):
+            raise
+        if rank == 0:
+            print(f"bench: {err}; using pack + NCCL all-to-all + unpack", file=sys.stderr, flush=True)
+        args.exchange = "nccl"
+        exchange = NcclExchange(dist, mem, world, rank)
+        dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
     if world > 1 and args.exchange == "loopback":
         # the slots other ranks would fill must not stay zero: attention's cost and power draw
         # depend on the data (rescale decisions, switching activity)

@@ -36,22 +36,33 @@ class PeerExchange:
         lib, gpu = self.gpu.lib, self.gpu
         handle = (C.c_ubyte * 64)()
         block = lib.h3x_peer_alloc(gpu.handle, nbytes, handle)
-        if not block:
-            raise H3Error(f"h3x_peer_alloc failed: {gpu.error()}")
-        self._blocks.append(block)
+        problem = None if block else f"h3x_peer_alloc failed: {gpu.error()}"
+        if block:
+            self._blocks.append(block)
         if self.loopback:
+            if problem:
+                raise H3Error(problem)
             return [block] * self.world
-        handles = self._all_gather(bytes(handle))
+        # every rank takes part in both host collectives whatever happened locally, and all
+        # ranks fail together: nobody is left waiting in a collective
+        handles = self._all_gather(bytes(handle) if block else None)
         out = []
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                out.append(block)
-                continue
-            mapped = lib.h3x_peer_open(gpu.handle, (C.c_ubyte * 64).from_buffer_copy(h))
-            if not mapped:
-                raise H3Error(f"h3x_peer_open failed: {gpu.error()}")
-            self._mapped.append(mapped)
-            out.append(mapped)
+        if problem is None and all(h is not None for h in handles):
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    out.append(block)
+                    continue
+                mapped = lib.h3x_peer_open(gpu.handle, (C.c_ubyte * 64).from_buffer_copy(h))
+                if not mapped:
+                    problem = f"h3x_peer_open failed: {gpu.error()}"
+                    break
+                self._mapped.append(mapped)
+                out.append(mapped)
+        elif problem is None:
+            problem = "a peer could not allocate its buffer"
+        problems = [p for p in self._all_gather(problem) if p]
+        if problems:
+            raise H3Error("peer-mapped buffers unavailable: " + problems[0])
         return out
 
     def setup(self, rows_local: int, heads: int, head_dim: int) -> dict[str, Tensor]:
