@@ -10,14 +10,22 @@
  * tcgen05.mma (M128 N256 K16, cta_group::1) with the F32 accumulator in
  * tensor memory; the accumulator is double-buffered (2 x 256 columns) so that
  * warps 2-5 drain tile i (tcgen05.ld, BF16 rounding, 16-byte stores) while the
- * tensor core already works on tile i+1. Tiles are walked in groups of 16
- * row-blocks so the CTAs that run together share operand slabs in L2.
+ * tensor core already works on tile i+1. Tiles are walked in groups of row
+ * blocks sized to ~40 MB of X, so the CTAs that run together share operand
+ * slabs in L2 and the weight streams from HBM once per group.
  *
- * Epilogue variants: plain store (+bias), and SwiGLU for the MLP up
- * projection, where a tile holds 128 gate columns and the matching 128 up
- * columns so the [rows, 2*hidden] intermediate never goes to memory. The
- * rounding points are the reference's: the fc1 result is rounded to BF16,
- * then silu(gate)*up is rounded to BF16 (h3_cuda_core.cu:1067-1110).
+ * The same kernel exists for CTA pairs (h3b_gemm_pair: clusters of two,
+ * tcgen05.mma.cta_group::2, 256 x 256 tiles, each CTA loads half of the weight
+ * tile); it is chosen for problems of up to 8,192 rows when the 256-row
+ * granularity costs no extra round of tiles.
+ *
+ * Epilogue variants: plain store (+bias); SwiGLU for the MLP up projection,
+ * where a tile holds 128 gate columns and the matching 128 up columns so the
+ * [rows, 2*hidden] intermediate never goes to memory (rounding points as in the
+ * reference: the fc1 result is rounded to BF16, then silu(gate)*up is rounded
+ * to BF16, h3_cuda_core.cu:1067-1110); and the grouped QKV projection with
+ * per-head RMSNorm and RoPE, which writes q, k and v directly (locally or into
+ * the owning rank's buffers for sequence parallelism).
  *
  * Every wait on an mbarrier is bounded: a thread that sees no progress for
  * about a second records H3B_STATUS_GEMM_TIMEOUT, tells the rest of the CTA
