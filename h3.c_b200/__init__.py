@@ -12,7 +12,8 @@ The directory name contains a dot, so import it through `__graft_entry__.load_pa
 from .binding import (BF16, F32, I8, U32, Gpu, H3Error, Tensor, UlyssesPeers,  # noqa: F401
                       declared_functions, library)
 from .peers import PeerExchange  # noqa: F401
-from .dit import (BlockWeights, DenoiseStep, Dit, DitShape, EulerSampler, extrapolation_ratio, reuse_schedule,
+from .dit import (BlockWeights, DenoiseStep, Dit, DitShape, EulerSampler, TokenReduction, extrapolation_ratio,
+                  reuse_schedule,
                   serving_sigmas, block_tensor_shapes,  # noqa: F401
                   default_inv_freq, grid_positions, row_map_for, shard_rows,
                   ulysses_pack_order)

@@ -119,6 +119,9 @@ class Dit:
         self.rows_local, self.row_begin, self.rows_valid = shard_rows(sequence, world,
                                                                       self.exchange.rank)
         rows, s = self.rows_local, shape
+        # rows the block ops work on: all local rows, or the pooled rows while a token
+        # reduction is active (single rank only)
+        self.active_rows, self.active_sequence = rows, sequence
         new = alloc or (lambda n: gpu.new(n, BF16))
         self.hidden = new(rows * s.hidden)
         self.mod_attention = new(rows * s.hidden)
@@ -151,7 +154,7 @@ class Dit:
         ex = self.exchange
         if ex.world == 1:
             g.op("sdpa_bf16", self.attention_heads, self.query, self.key, self.value,
-                 self.sequence, s.heads, s.head_dim, s.scale)
+                 self.active_sequence, s.heads, s.head_dim, s.scale)
             return
         hpr = s.heads // ex.world
         for src, dst in zip((self.query, self.key, self.value), self.send):
@@ -170,7 +173,7 @@ class Dit:
                   adaln_ready: bool, next_w: BlockWeights | None) -> bool:
         """One block; returns whether the next block's attention adaLN is already in
         mod_attention (the cross-block fusion of h3_dit.c:2139-2177)."""
-        g, s, rows = self.gpu, self.s, self.rows_local
+        g, s, rows = self.gpu, self.s, self.active_rows
         if not adaln_ready:
             g.op("adaln_bf16", self.mod_attention, self.hidden, w.norm1, w.modulation, row_map,
                  rows, s.hidden, s.slots, 0, 1, s.eps)
@@ -204,13 +207,120 @@ class Dit:
         return False
 
     def run_blocks(self, blocks: list[BlockWeights], row_map: Tensor, rope_cos: Tensor,
-                   rope_sin: Tensor) -> None:
+                   rope_sin: Tensor, reduction: "TokenReduction | None" = None,
+                   reduced_row_map: Tensor | None = None) -> None:
+        """All blocks. With `reduction`, blocks [begin, end) run on the pooled token grid
+        (h3_dit.c:2316-2345): pool before block `begin`, expand before block `end` (or after the
+        last block); the cross-block adaLN fusion is not carried over either boundary."""
+        red = reduction
+        if red is not None and self.exchange.world != 1:
+            raise ValueError("token reduction is not combined with sequence parallelism")
         ready = False
         for i, w in enumerate(blocks):
-            nxt = blocks[i + 1] if i + 1 < len(blocks) else None
-            ready = self.run_block(w, row_map, rope_cos, rope_sin, ready, nxt)
+            if red is not None and i == red.begin:
+                self._enter_reduction(red)
+                ready = False
+            if red is not None and i == red.end:
+                self._leave_reduction(red)
+                ready = False
+            boundary = red is not None and i + 1 in (red.begin, red.end)
+            nxt = blocks[i + 1] if i + 1 < len(blocks) and not boundary else None
+            if red is not None and red.active:
+                ready = self.run_block(w, reduced_row_map, red.rope_cos, red.rope_sin, ready, nxt)
+            else:
+                ready = self.run_block(w, row_map, rope_cos, rope_sin, ready, nxt)
             if i == int(len(blocks) * 0.6):
                 self.gpu.flush()     # the reference's mid-step command split (h3_dit.c:2403-2406)
+        if red is not None and red.active:
+            self._leave_reduction(red)
+
+    def _enter_reduction(self, red: "TokenReduction") -> None:
+        """enter_token_reduction (h3_dit.c:1921-1937): snapshot the full rows, pool horizontally
+        adjacent video tokens into attention_output, which becomes the hidden state."""
+        s = self.s
+        self.gpu.op("token_pool_bf16", self.attention_output, self.hidden, 0, red.original, 0,
+                    red.baseline, 0, red.baseline_indices, red.pool_pairs, self.sequence,
+                    red.reduced_sequence, red.baseline_rows, s.hidden)
+        self.hidden, self.attention_output = self.attention_output, self.hidden
+        self.active_rows = self.active_sequence = red.reduced_sequence
+        red.active = True
+
+    def _leave_reduction(self, red: "TokenReduction") -> None:
+        """leave_token_reduction (h3_dit.c:1963-1981): every full row gets its snapshot plus
+        update_scale times what its pooled parent gained; the result lands in mod_attention,
+        which becomes the hidden state."""
+        s = self.s
+        self.gpu.op("token_expand_delta_bf16", self.mod_attention, red.original, 0, self.hidden,
+                    red.baseline, 0, red.baseline_indices, red.expand_parents, self.sequence,
+                    red.reduced_sequence, red.baseline_rows, s.hidden, red.video_start,
+                    float(red.scale))
+        self.hidden, self.mod_attention = self.mod_attention, self.hidden
+        self.active_rows, self.active_sequence = self.rows_local, self.sequence
+        red.active = False
+
+
+class TokenReduction:
+    """Maps and buffers of the reference's token-reduction mode (h3_dit.c:440-505, 1258-1310):
+    between blocks `begin` and `end` every pair of horizontally adjacent video tokens is
+    averaged into one (an odd last column stays single); text / conditioning rows before the
+    target video are kept. The video must end the row layout.
+
+    video grid: t x h x w tokens (the reference's latent_t x latent_h/2 x latent_w/2)."""
+
+    def __init__(self, gpu: Gpu, shape: DitShape, *, sequence: int, video_start: int, t: int,
+                 h: int, w: int, begin: int, end: int, scale: float = 1.0):
+        if video_start + t * h * w != sequence or not (0 <= begin < end):
+            raise ValueError("the target video must end the row layout and begin < end")
+        self.begin, self.end, self.scale, self.video_start = begin, end, scale, video_start
+        self.sequence, self.width = sequence, w
+        self.reduced_width = (w + 1) // 2
+        self.reduced_sequence = video_start + t * h * self.reduced_width
+        self.baseline_rows = t * h * w - t * h * self.reduced_width
+        self.pairs = np.array([self.pool_sources(r) for r in range(self.reduced_sequence)],
+                              np.uint32)
+        merged = (np.arange(self.reduced_sequence) >= video_start) & (self.pairs[:, 0] != self.pairs[:, 1])
+        indices = np.full(self.reduced_sequence, 0xFFFFFFFF, np.uint32)
+        indices[merged] = np.arange(int(merged.sum()), dtype=np.uint32)
+        if int(merged.sum()) != self.baseline_rows:
+            raise ValueError("token-reduction baseline map is inconsistent")
+        self.baseline_index_values = indices
+        self.parents = np.array([self.reduced_parent(r) for r in range(sequence)], np.uint32)
+        self.pool_pairs = gpu.u32(self.pairs.reshape(-1))
+        self.baseline_indices = gpu.u32(indices)
+        self.expand_parents = gpu.u32(self.parents)
+        self.original = gpu.new(sequence * shape.hidden, BF16)
+        self.baseline = gpu.new(max(1, self.baseline_rows) * shape.hidden, BF16)
+        self.rope_cos = self.rope_sin = None
+        self.active = False
+
+    def pool_sources(self, reduced_row: int) -> tuple[int, int]:
+        """token_pool_sources (h3_dit.c:478-494)."""
+        if reduced_row < self.video_start:
+            return reduced_row, reduced_row
+        local = reduced_row - self.video_start
+        source = self.video_start + (local // self.reduced_width) * self.width + \
+            (local % self.reduced_width) * 2
+        second = source + (1 if (source - self.video_start) % self.width + 1 < self.width else 0)
+        return source, second
+
+    def reduced_parent(self, full_row: int) -> int:
+        """token_reduced_parent (h3_dit.c:496-503)."""
+        if full_row < self.video_start:
+            return full_row
+        local = full_row - self.video_start
+        return self.video_start + (local // self.width) * self.reduced_width + (local % self.width) // 2
+
+    def reduced_positions(self, positions: np.ndarray) -> np.ndarray:
+        """Positions of the pooled rows: the mean of their two sources (h3_dit.c:930-940)."""
+        return ((positions[self.pairs[:, 0]].astype(np.float64) +
+                 positions[self.pairs[:, 1]].astype(np.float64)) * 0.5).astype(np.float32)
+
+    def reduced_row_map(self, row_map: np.ndarray) -> np.ndarray:
+        """Modulation row of a pooled row = that of its first source (h3_dit.c:1164-1171)."""
+        return np.ascontiguousarray(row_map[self.pairs[:, 0]], np.uint32)
+
+    def set_rope(self, rope_cos: Tensor, rope_sin: Tensor) -> None:
+        self.rope_cos, self.rope_sin = rope_cos, rope_sin
 
 
 class DenoiseStep:
