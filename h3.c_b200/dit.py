@@ -208,21 +208,21 @@ class Dit:
 
     def run_blocks(self, blocks: list[BlockWeights], row_map: Tensor, rope_cos: Tensor,
                    rope_sin: Tensor, reduction: "TokenReduction | None" = None,
-                   reduced_row_map: Tensor | None = None) -> None:
+                   reduced_row_map: Tensor | None = None, fused_boundaries: bool = True) -> None:
         """All blocks. With `reduction`, blocks [begin, end) run on the pooled token grid
         (h3_dit.c:2316-2345): pool before block `begin`, expand before block `end` (or after the
-        last block); the cross-block adaLN fusion is not carried over either boundary."""
+        last block); the cross-block adaLN fusion is not carried over either boundary. With
+        fused_boundaries (the reference's default) the pool / expand kernel also applies the
+        attention adaLN of the block that follows."""
         red = reduction
         if red is not None and self.exchange.world != 1:
             raise ValueError("token reduction is not combined with sequence parallelism")
         ready = False
         for i, w in enumerate(blocks):
             if red is not None and i == red.begin:
-                self._enter_reduction(red)
-                ready = False
+                ready = self._enter_reduction(red, w if fused_boundaries else None, reduced_row_map)
             if red is not None and i == red.end:
-                self._leave_reduction(red)
-                ready = False
+                ready = self._leave_reduction(red, w if fused_boundaries else None, row_map)
             boundary = red is not None and i + 1 in (red.begin, red.end)
             nxt = blocks[i + 1] if i + 1 < len(blocks) and not boundary else None
             if red is not None and red.active:
@@ -234,29 +234,51 @@ class Dit:
         if red is not None and red.active:
             self._leave_reduction(red)
 
-    def _enter_reduction(self, red: "TokenReduction") -> None:
-        """enter_token_reduction (h3_dit.c:1921-1937): snapshot the full rows, pool horizontally
-        adjacent video tokens into attention_output, which becomes the hidden state."""
+    def _enter_reduction(self, red: "TokenReduction", w: BlockWeights | None = None,
+                         reduced_row_map: Tensor | None = None) -> bool:
+        """enter_token_reduction / enter_token_reduction_adaln (h3_dit.c:1921-1961): snapshot
+        the full rows, pool horizontally adjacent video tokens into attention_output, which
+        becomes the hidden state; with the next block's weights also its attention adaLN into
+        mod_attention. Returns whether that adaLN is ready."""
         s = self.s
-        self.gpu.op("token_pool_bf16", self.attention_output, self.hidden, 0, red.original, 0,
-                    red.baseline, 0, red.baseline_indices, red.pool_pairs, self.sequence,
-                    red.reduced_sequence, red.baseline_rows, s.hidden)
+        if w is None:
+            self.gpu.op("token_pool_bf16", self.attention_output, self.hidden, 0, red.original, 0,
+                        red.baseline, 0, red.baseline_indices, red.pool_pairs, self.sequence,
+                        red.reduced_sequence, red.baseline_rows, s.hidden)
+        else:
+            self.gpu.op("token_pool_adaln_bf16", self.attention_output, self.mod_attention,
+                        self.hidden, 0, red.original, 0, red.baseline, 0, red.baseline_indices,
+                        red.pool_pairs, w.norm1, w.modulation, reduced_row_map, self.sequence,
+                        red.reduced_sequence, red.baseline_rows, s.hidden, s.slots, 0, 1, s.eps)
         self.hidden, self.attention_output = self.attention_output, self.hidden
         self.active_rows = self.active_sequence = red.reduced_sequence
         red.active = True
+        return w is not None
 
-    def _leave_reduction(self, red: "TokenReduction") -> None:
-        """leave_token_reduction (h3_dit.c:1963-1981): every full row gets its snapshot plus
-        update_scale times what its pooled parent gained; the result lands in mod_attention,
-        which becomes the hidden state."""
+    def _leave_reduction(self, red: "TokenReduction", w: BlockWeights | None = None,
+                         row_map: Tensor | None = None) -> bool:
+        """leave_token_reduction / leave_token_reduction_adaln (h3_dit.c:1963-2006): every full
+        row gets its snapshot plus update_scale times what its pooled parent gained. Plain form:
+        the result lands in mod_attention, which becomes the hidden state. Fused form: the result
+        lands in attention_output (the new hidden state) and the next block's attention adaLN in
+        mod_attention."""
         s = self.s
-        self.gpu.op("token_expand_delta_bf16", self.mod_attention, red.original, 0, self.hidden,
-                    red.baseline, 0, red.baseline_indices, red.expand_parents, self.sequence,
-                    red.reduced_sequence, red.baseline_rows, s.hidden, red.video_start,
-                    float(red.scale))
-        self.hidden, self.mod_attention = self.mod_attention, self.hidden
+        if w is None:
+            self.gpu.op("token_expand_delta_bf16", self.mod_attention, red.original, 0, self.hidden,
+                        red.baseline, 0, red.baseline_indices, red.expand_parents, self.sequence,
+                        red.reduced_sequence, red.baseline_rows, s.hidden, red.video_start,
+                        float(red.scale))
+            self.hidden, self.mod_attention = self.mod_attention, self.hidden
+        else:
+            self.gpu.op("token_expand_adaln_bf16", self.attention_output, self.mod_attention,
+                        red.original, 0, self.hidden, red.baseline, 0, red.baseline_indices,
+                        red.expand_parents, w.norm1, w.modulation, row_map, self.sequence,
+                        red.reduced_sequence, red.baseline_rows, s.hidden, red.video_start,
+                        float(red.scale), s.slots, 0, 1, s.eps)
+            self.hidden, self.attention_output = self.attention_output, self.hidden
         self.active_rows, self.active_sequence = self.rows_local, self.sequence
         red.active = False
+        return w is not None
 
 
 class TokenReduction:

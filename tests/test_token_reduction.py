@@ -45,8 +45,9 @@ def test_layout_must_end_with_the_video(pkg):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fused", [True, False])  # pool / expand kernels with or without the next adaLN
 @pytest.mark.parametrize("end", [3, 4])          # leave before the last block / after the last block
-def test_reduced_block_range_matches_oracle(pkg, end):
+def test_reduced_block_range_matches_oracle(pkg, end, fused):
     hidden, heads, ffn, n_blocks = 512, 4, 1024, 4
     text_rows, t, h, w = 24, 2, 6, 9
     rows = text_rows + t * h * w
@@ -82,7 +83,7 @@ def test_reduced_block_range_matches_oracle(pkg, end):
         dit.hidden.write(x)
         gpu.begin()
         dit.run_blocks(weights, gpu.u32(row_map), gpu.bf16(cos), gpu.bf16(sin), reduction=red,
-                       reduced_row_map=gpu.u32(red.reduced_row_map(row_map)))
+                       reduced_row_map=gpu.u32(red.reduced_row_map(row_map)), fused_boundaries=fused)
         gpu.submit()
         got = dit.hidden.read()[:rows * hidden]
     finally:
@@ -103,5 +104,5 @@ def test_reduced_block_range_matches_oracle(pkg, end):
     want = run(want, end, n_blocks, rows, row_map, cos, sin)
     g, wv = o.from_bf16(got).astype(np.float64), o.from_bf16(want).astype(np.float64)
     rel, mx = np.linalg.norm(g - wv) / np.linalg.norm(wv), np.abs(g - wv).max()
-    print(f"token reduction blocks [1,{end}): rel_l2={rel:.3e} max_abs={mx:.3e}")
+    print(f"token reduction blocks [1,{end}) fused={fused}: rel_l2={rel:.3e} max_abs={mx:.3e}")
     assert rel <= 1e-2 and mx <= 1e-1
