@@ -816,7 +816,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
     if (sparse && !(hd == AT_D && aligned && !simt && scale > 0.0f))
         return h3b_fail(gpu, "the block-sparse mask needs head_dim 128, aligned tensors and the tensor-core kernel");
     if (hd == AT_D && aligned && !simt && scale > 0.0f) {
-        static bool configured = false;
+        static bool configured_on[64];      /* the attribute is per device */
+        bool &configured = configured_on[gpu->device & 63];
         if (!configured) {
             bool ok = true;
             for (auto *kernel : {h3b_sdpa_tc<false, false>, h3b_sdpa_tc<false, true>,

@@ -671,9 +671,13 @@ bool env_flag(const char *name) {
 /* How many CTA pairs of the paired kernel the device keeps resident at once (0: clusters of two
  * cannot be scheduled, or the kernel cannot get its shared memory); queried once per epilogue. */
 template <int EPI>
-int max_resident_pairs() {
-    static int pairs = -1;
-    if (pairs >= 0) return pairs;
+int max_resident_pairs(int device) {
+    /* function attributes and occupancy belong to a device: one answer per device */
+    static int per_device[64];
+    static bool known[64];
+    int &pairs = per_device[device & 63];
+    if (known[device & 63]) return pairs;
+    known[device & 63] = true;
     pairs = 0;
     if (cudaFuncSetAttribute(h3b_gemm_pair<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(pair_smem<EPI>())) != cudaSuccess) {
@@ -706,7 +710,8 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t weight_rows,
               uint32_t out_cols, uint32_t tiles_n, uint32_t up_offset,
               const TcArgs *extra = nullptr) {
-    static bool configured = false;
+    static bool configured_on[64];      /* the attribute is per device */
+    bool &configured = configured_on[gpu->device & 63];
     constexpr size_t smem_bytes = EPI == H3B_EPI_QKV_ROPE ? TC_SMEM_QKV : TC_SMEM;
     if (!configured) {
         if (cudaFuncSetAttribute(h3b_gemm_tc<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -747,7 +752,7 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
      * co-schedule clusters of two, and X fits in L2: measured inside the power-capped step, pairs
      * win at 6,400 rows (258 vs 265 ms per 50-block step), make no difference at 12,619 rows and
      * lose at 50,476 rows (1,070 vs 1,024 ms per 10 blocks), where X streams from HBM as well. */
-    const int pairs = max_resident_pairs<EPI>();
+    const int pairs = max_resident_pairs<EPI>(gpu->device);
     bool pair_size = false;
     if (pairs > 0 && rows > BM) {
         const uint64_t lone_rounds = (uint64_t(args.tiles_m) * tiles_n + gpu->sm_count - 1) / gpu->sm_count;
