@@ -24,7 +24,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from .binding import BF16, F32, U32, Gpu, Tensor
+from .binding import BF16, F32, Gpu, Tensor
 
 
 @dataclass

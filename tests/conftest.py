@@ -2,8 +2,6 @@
 import sys
 from pathlib import Path
 
-import pytest
-
 ROOT = Path(__file__).resolve().parent.parent
 for p in (ROOT, ROOT / "oracle"):
     if str(p) not in sys.path:
