@@ -33,6 +33,10 @@ extern "C" {
 #endif
 
 /* ---- types: h3_gpu.h:7-33 ------------------------------------------- */
+/* When the reference's own header was included first (its guard is H3_GPU_H), its type
+ * definitions are used and every prototype below is checked against its declaration by the
+ * compiler: a mismatch in any argument or return type is a compile error. */
+#ifndef H3_GPU_H
 typedef struct h3_gpu h3_gpu;
 typedef struct h3_gpu_tensor h3_gpu_tensor;
 
@@ -47,6 +51,7 @@ typedef struct {
     uint64_t blit_copies, submissions;
     double command_encode_seconds, command_wait_seconds, gpu_seconds;
 } h3_gpu_stats;
+#endif /* H3_GPU_H */
 
 /* ---- context: h3_gpu.h:35-51,100-110; h3_gpu_cuda.cu:80-170,871-933 --- */
 h3_gpu *h3_gpu_create(const char *unused_shader_path, char *error, size_t error_size);

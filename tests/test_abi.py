@@ -68,3 +68,50 @@ def test_product_does_not_reference_the_oracle():
             assert "h3_oracle" not in text and "oracle/" not in text, path
     needed = subprocess.run(["ldd", str(LIB)], capture_output=True, text=True).stdout
     assert "oracle" not in needed
+
+
+def test_prototypes_agree_with_the_reference_header(tmp_path):
+    """Both headers in one C11 translation unit: the compiler rejects any prototype of
+    include/h3b200.h whose argument or return types differ from the reference's declaration."""
+    if not REFERENCE_HEADER.exists():
+        pytest.skip("the reference tree is not present")
+    import subprocess
+    src = tmp_path / "both.c"
+    src.write_text('#include "h3_gpu.h"\n#include "h3b200.h"\nint main(void) { return 0; }\n')
+    res = subprocess.run(["gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-I", str(REFERENCE_HEADER.parent),
+                          "-I", str(ROOT / "include"), "-c", str(src), "-o", str(tmp_path / "both.o")],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]
+
+
+def test_a_c_host_links_and_fails_loudly_without_a_device(tmp_path):
+    """A plain C11 host built against include/h3b200.h and linked with libh3b200.so: on a machine
+    without a GPU h3_gpu_create returns NULL with a message (no CPU fallback)."""
+    import subprocess
+    import torch
+    src = tmp_path / "host.c"
+    src.write_text('''
+#include <stdio.h>
+#include "h3b200.h"
+int main(void) {
+    char error[256] = {0};
+    h3_gpu *gpu = h3_gpu_create(NULL, error, sizeof(error));
+    if (!gpu) { printf("create failed: %s\\n", error); return 3; }
+    h3_gpu_tensor *t = h3_gpu_tensor_new_bf16(gpu, 64);
+    int ok = t && h3_gpu_begin(gpu) && h3_gpu_add_bf16(gpu, t, t, t, 64) && h3_gpu_submit(gpu);
+    h3_gpu_tensor_free(t);
+    h3_gpu_free(gpu);
+    printf("ran: %d\\n", ok);
+    return ok ? 0 : 4;
+}
+''')
+    exe = tmp_path / "host"
+    res = subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(src), "-o", str(exe),
+                          "-L", str(LIB.parent), "-lh3b200", f"-Wl,-rpath,{LIB.parent}"],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    if torch.cuda.is_available():
+        assert run.returncode == 0 and "ran: 1" in run.stdout, run.stdout + run.stderr
+    else:
+        assert run.returncode == 3 and "create failed:" in run.stdout and len(run.stdout.strip()) > 16
