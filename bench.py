@@ -49,9 +49,11 @@ WORKLOADS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel, from the
-# ncu capture summarised in profiles/h3b_gemm_tc_dram_traffic_c3.md; (workload, ranks) -> bytes
-NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 1050.3e6}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel from an ncu
+# capture of this file's default command; (workload, ranks) -> bytes. Empty until a capture of
+# the current tile walk exists: the line then carries "traffic": null.
+NCU_DRAM_BYTES_PER_LAUNCH = {}
+NCU_DRAM_SOURCE = None
 
 
 def measured_peaks():
@@ -74,6 +76,9 @@ def cpu_sample(shape, sequence, gemm_rows=256, attn_rows=128):
     query rows). Returns (ms per step extrapolated, description, threads, seconds spent)."""
     sys.path.insert(0, str(ROOT / "oracle"))
     import h3_oracle as o
+    # a launcher may have exported OMP_NUM_THREADS=1 (torch.distributed.run does): the baseline
+    # uses every core this process may run on
+    o.set_threads(len(os.sched_getaffinity(0)))
     s = shape
     rng = np.random.default_rng(0)
 
@@ -117,7 +122,7 @@ def cpu_sample(shape, sequence, gemm_rows=256, attn_rows=128):
 REF_CUDA = ROOT / "oracle" / "_ref" / "libh3ref.so"
 
 
-def reference_cuda_block(shape, sequence, text_rows, repeats=3):
+def reference_cuda_block(shape, sequence, text_rows, repeats=10):
     """One DiT block at the workload's S through the reference's own CUDA backend (its sources
     compiled as a checker under oracle/_ref: cuBLASLt GEMMs, mma.sync attention, unfused row
     kernels), driven by the same host sequence: the kernel path to beat on the same GPU.
@@ -265,90 +270,25 @@ class ClockSampler:
 
 # ------------------------------------------------------------------- GPU arm
 
-class TorchMemory:
-    """Device memory from torch (caching allocator), wrapped into library tensors."""
-
-    def __init__(self, torch, pkg, gpu, device):
-        self.torch, self.pkg, self.gpu, self.device = torch, pkg, gpu, device
-        self.by_handle = {}
-
-    def bf16(self, elements, fill=None, std=None, generator=None):
-        t = self.torch.empty(max(1, elements), dtype=self.torch.bfloat16, device=self.device)
-        if std is not None:
-            t.normal_(0.0, std, generator=generator)
-        elif fill is not None:
-            t.fill_(fill)
-        else:
-            t.zero_()
-        wrapped = self.gpu.wrap(t.data_ptr(), elements, self.pkg.BF16)
-        self.by_handle[wrapped.handle] = t
-        return wrapped
-
-    def f32(self, elements, std=None, generator=None):
-        t = self.torch.zeros(max(1, elements), dtype=self.torch.float32, device=self.device)
-        if std is not None:
-            t.normal_(0.0, std, generator=generator)
-        wrapped = self.gpu.wrap(t.data_ptr(), elements, self.pkg.F32)
-        self.by_handle[wrapped.handle] = t
-        return wrapped
-
-    def torch_of(self, tensor):
-        """torch view of a library tensor: the torch allocation it wraps, else a zero-copy byte
-        view of the library's own allocation through the CUDA array interface (bytes, because
-        the collectives this is used for do not take 16-bit integers)."""
-        if tensor.handle not in self.by_handle:
-            size = {self.pkg.BF16: 2, self.pkg.F32: 4}[tensor.dtype]
-
-            class _Span:
-                __cuda_array_interface__ = {
-                    "shape": (tensor.elements * size,), "version": 2, "typestr": "|u1",
-                    "data": (tensor.pointer, False)}
-            view = self.torch.as_tensor(_Span(), device=self.device)
-            self.by_handle[tensor.handle] = view
-        return self.by_handle[tensor.handle]
+class Weights:
+    """Random-init weights of the architecture, shared by every workload of a run."""
 
 
-class NcclExchange:
-    """all-to-all of equal blocks over NCCL (torch.distributed), on torch's current stream."""
-
-    def __init__(self, dist, memory, world, rank):
-        self.dist, self.memory, self.world, self.rank = dist, memory, world, rank
-        self.calls = 0
-
-    def all_to_all(self, out, inp):
-        self.dist.all_to_all_single(self.memory.torch_of(out), self.memory.torch_of(inp))
-        self.calls += 1
-
-
-class NcclPair:
-    """Velocity swap between the two classifier-free-guidance groups: rank i of the cond group
-    and rank i of the uncond group exchange their local velocity rows over NCCL."""
-
-    def __init__(self, dist, memory, partner, is_cond):
-        self.dist, self.memory, self.partner, self.is_cond = dist, memory, partner, is_cond
-
-    def swap(self, out, inp):
-        d = self.dist
-        ops = [d.P2POp(d.isend, self.memory.torch_of(inp), self.partner),
-               d.P2POp(d.irecv, self.memory.torch_of(out), self.partner)]
-        for req in d.batch_isend_irecv(ops):
-            req.wait()
-
-
-def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed=0, time_rows=2,
-                text_seed=None):
-    """Random-init weights of the architecture, modulation tables computed by the adaLN
-    projection (rows = time rows, 2688 -> 3*6*5376, the load-time GEMM of the reference's
-    h3_dit_schedule_precompute), rope tables and row maps for this rank's rows."""
+def build_weights(torch, pkg, gpu, mem, shape, time_rows=2, seed=0):
+    """50 blocks (770 MB each), modulation tables computed by the adaLN projection (rows = time
+    rows, 2688 -> 3*6*5376: the load-time GEMM of the reference's h3_dit_schedule_precompute,
+    h3_dit_schedule.c:264-301), final head and patch projection."""
     s = shape
+    w = Weights()
+    w.time_rows = time_rows
     gen = torch.Generator(device=mem.device)
     gen.manual_seed(seed)
-    dit = pkg.Dit(gpu, s, sequence, exchange=exchange, alloc=lambda n: mem.bf16(n))
-    silu_time = mem.bf16(time_rows * s.time_dim, std=0.125, generator=gen)   # modulation std ~0.13
+    w.generator = gen
+    w.silu_time = mem.bf16(time_rows * s.time_dim, std=0.125, generator=gen)   # modulation std ~0.13
     mod_cols = s.modalities * s.slots * s.hidden
-    proj_w = mem.bf16(mod_cols * s.time_dim)
-    proj_b = mem.bf16(mod_cols)
-    blocks = []
+    w.proj_w = mem.bf16(mod_cols * s.time_dim)
+    w.proj_b = mem.bf16(mod_cols)
+    w.blocks = []
     for _ in range(s.blocks):
         t = {}
         for name, count in pkg.block_tensor_shapes(s, time_rows * s.modalities).items():
@@ -358,38 +298,48 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
                 t[name] = mem.bf16(count)
             else:
                 t[name] = mem.bf16(count, std=0.02, generator=gen)
-        mem.torch_of(proj_w).normal_(0.0, 0.02, generator=gen)
-        mem.torch_of(proj_b).normal_(0.0, 0.02, generator=gen)
+        mem.torch_of(w.proj_w).normal_(0.0, 0.02, generator=gen)
+        mem.torch_of(w.proj_b).normal_(0.0, 0.02, generator=gen)
         gpu.begin()
-        gpu.op("linear_bf16", t["modulation"], silu_time, proj_w, proj_b, time_rows, s.time_dim, mod_cols)
+        gpu.op("linear_bf16", t["modulation"], w.silu_time, w.proj_w, w.proj_b, time_rows, s.time_dim, mod_cols)
         gpu.submit()
-        blocks.append(pkg.BlockWeights(**t))
-    final_mod = mem.bf16(time_rows * s.final_slots * s.hidden, std=0.3, generator=gen)
-    final_w = mem.bf16(s.video_patch * s.hidden, std=0.02, generator=gen)
-    final_b = mem.bf16(s.video_patch, std=0.02, generator=gen)
-    final_norm = mem.bf16(s.hidden, fill=1.0)
-    patch_w = mem.f32(s.hidden * s.video_patch, std=0.02, generator=gen)
-    patch_b = mem.f32(s.hidden, std=0.02, generator=gen)
-    text_gen = gen
-    if text_seed is not None:
-        text_gen = torch.Generator(device=mem.device)
-        text_gen.manual_seed(text_seed)
-    text_hidden = mem.bf16(max(1, text_rows) * s.hidden, std=1.0, generator=text_gen)
+        w.blocks.append(pkg.BlockWeights(**t))
+    w.final_mod = mem.bf16(time_rows * s.final_slots * s.hidden, std=0.3, generator=gen)
+    w.final_w = mem.bf16(s.video_patch * s.hidden, std=0.02, generator=gen)
+    w.final_b = mem.bf16(s.video_patch, std=0.02, generator=gen)
+    w.final_norm = mem.bf16(s.hidden, fill=1.0)
+    w.patch_w = mem.f32(s.hidden * s.video_patch, std=0.02, generator=gen)
+    w.patch_b = mem.f32(s.hidden, std=0.02, generator=gen)
+    return w
 
-    # this rank's slice of the global rows: text rows first, then video rows
-    r0, rows = dit.row_begin, dit.rows_local
+
+def workload_positions(sequence, text_rows, padded_rows):
+    """(t, h, w) per global row: text rows (index, 0, 0), then video rows on a t x 32 x 32 grid."""
     video_rows_total = sequence - text_rows
-    sys.path.insert(0, str(ROOT / "oracle"))
-    world = dit.exchange.world
-    pos = np.zeros((dit.rows_local * world, 3), np.float32)
+    pos = np.zeros((padded_rows, 3), np.float32)
     pos[:text_rows, 0] = np.arange(text_rows)
     idx = np.arange(video_rows_total)
     pos[text_rows:sequence, 0] = idx // 1024 if video_rows_total >= 1024 else 0
     pos[text_rows:sequence, 1] = (idx % 1024) // 32
     pos[text_rows:sequence, 2] = idx % 32
-    inv_freq = pkg.default_inv_freq()
+    return pos
+
+
+def build_workload(torch, pkg, gpu, mem, shape, w, sequence, text_rows, exchange, text_seed=None):
+    """Activations, rope tables, row maps and the denoise step of one workload (this rank's row
+    slice: text rows first, then video rows) on the shared weights."""
+    s = shape
+    dit = pkg.Dit(gpu, s, sequence, exchange=exchange, alloc=lambda n: mem.bf16(n))
+    text_gen = w.generator
+    if text_seed is not None:
+        text_gen = torch.Generator(device=mem.device)
+        text_gen.manual_seed(text_seed)
+    text_hidden = mem.bf16(max(1, text_rows) * s.hidden, std=1.0, generator=text_gen)
+    r0, rows = dit.row_begin, dit.rows_local
+    world = dit.exchange.world
+    pos = workload_positions(sequence, text_rows, dit.rows_local * world)
     local = pos[r0:r0 + rows]
-    ang = local[:, :, None] * inv_freq[None, None, :]          # [rows, 3 axes, 16 freqs]
+    ang = local[:, :, None] * pkg.default_inv_freq()[None, None, :]          # [rows, 3 axes, 16 freqs]
     cos = torch.from_numpy(np.cos(ang).reshape(rows, 48).astype(np.float32))
     sin = torch.from_numpy(np.sin(ang).reshape(rows, 48).astype(np.float32))
     rope_cos, rope_sin = mem.bf16(rows * 48), mem.bf16(rows * 48)
@@ -399,22 +349,23 @@ def build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange, seed
     tags[:text_rows] = 1
     local_text = max(0, min(text_rows, r0 + dit.rows_valid) - r0)
     local_video = dit.rows_valid - local_text
-    # one row map per time row (row_map[row] = time_row * 3 + modality tag); the single-step
-    # bench uses time row 1
-    row_maps = [gpu.u32(tags[r0:r0 + rows] + 3 * t) for t in range(time_rows)]
-    final_row_maps = [gpu.u32(np.full(max(1, local_video), t, np.uint32)) for t in range(time_rows)]
-    row_map, final_row_map = row_maps[1], final_row_maps[1]
-    step = pkg.DenoiseStep(dit, blocks, video_rows=local_video, text_rows=local_text,
-                           patch_weight=patch_w, patch_bias=patch_b, text_hidden=text_hidden,
-                           final_norm=final_norm, final_modulation=final_mod, final_weight=final_w,
-                           final_bias=final_b, row_map=row_map, final_row_map=final_row_map,
+    # one row map per time row (row_map[row] = time_row * 3 + modality tag); a single-step
+    # measurement uses time row 1
+    row_maps = [gpu.u32(tags[r0:r0 + rows] + 3 * t) for t in range(w.time_rows)]
+    final_row_maps = [gpu.u32(np.full(max(1, local_video), t, np.uint32)) for t in range(w.time_rows)]
+    step = pkg.DenoiseStep(dit, w.blocks, video_rows=local_video, text_rows=local_text,
+                           patch_weight=w.patch_w, patch_bias=w.patch_b, text_hidden=text_hidden,
+                           final_norm=w.final_norm, final_modulation=w.final_mod, final_weight=w.final_w,
+                           final_bias=w.final_b, row_map=row_maps[min(1, w.time_rows - 1)],
+                           final_row_map=final_row_maps[min(1, w.time_rows - 1)],
                            rope_cos=rope_cos, rope_sin=rope_sin)
     step.row_maps, step.final_row_maps = row_maps, final_row_maps
     return dit, step
 
 
-def time_kernel(torch, gpu, fn, flops, repeats=8):
-    """Average duration of one launch, CUDA events on the launching (default) stream."""
+def time_kernel(torch, gpu, fn, work, repeats=8):
+    """Average duration of one launch, CUDA events on the launching (default) stream.
+    Returns (ms, work per second / 1e12): TFLOP/s for flops, TB/s for bytes."""
     for _ in range(2):
         gpu.begin(); fn(); gpu.submit()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -426,7 +377,135 @@ def time_kernel(torch, gpu, fn, flops, repeats=8):
     gpu.submit()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / repeats
-    return ms, flops / (ms * 1e-3) / 1e12
+    return ms, work / (ms * 1e-3) / 1e12
+
+
+def kernel_timings(torch, pkg, gpu, shape, dit, step, exchange, sequence, world, repeats=8):
+    """The block's hot kernels timed alone on this rank's rows: name -> (ms, TFLOP/s)."""
+    s, rows, w = shape, dit.rows_local, step.blocks[0]
+    out = {}
+    qkv_flops = 2.0 * rows * s.hidden * 3 * s.inner
+    if dit.push:
+        def qkv_op():
+            gpu.op("h3x_grouped_qkv_linear_rope_push", exchange.peers, dit.mod_attention, w.qkv,
+                   w.q_norm, w.k_norm, step.rope_cos, step.rope_sin, rows, s.hidden, s.heads,
+                   s.head_dim, s.rope_half, s.eps)
+    else:
+        def qkv_op():
+            gpu.op("grouped_qkv_linear_rope_bf16", dit.query, dit.key, dit.value, dit.qkv,
+                   dit.mod_attention, w.qkv, w.q_norm, w.k_norm, step.rope_cos, step.rope_sin,
+                   rows, s.hidden, s.heads, s.head_dim, s.rope_half, s.eps)
+    out["qkv_proj_norm_rope"] = time_kernel(torch, gpu, qkv_op, qkv_flops, repeats)
+    # the MLP's two launches; the activation lands in the (idle) qkv buffer
+    out["mlp_fc1_swiglu"] = time_kernel(
+        torch, gpu, lambda: gpu.op("h3x_linear_swiglu_bf16", dit.qkv, dit.mod_attention, w.fc1, rows,
+                                   s.hidden, s.ffn), 2.0 * rows * s.hidden * 2 * s.ffn, repeats)
+    out["mlp_fc2"] = time_kernel(
+        torch, gpu, lambda: gpu.op("linear_bf16", dit.attention_output, dit.qkv, w.fc2, None, rows,
+                                   s.ffn, s.hidden), 2.0 * rows * s.ffn * s.hidden, repeats)
+    out["gemm_out_proj"] = time_kernel(
+        torch, gpu, lambda: gpu.op("linear_bf16", dit.attention_output, dit.attention_heads, w.out,
+                                   None, rows, s.inner, s.hidden), 2.0 * rows * s.inner * s.hidden, repeats)
+    if dit.push:
+        attn_flops = 4.0 * sequence * sequence * (s.heads // world) * s.head_dim
+        out["attention"] = time_kernel(
+            torch, gpu, lambda: gpu.op("h3x_sdpa_push", exchange.peers, dit.gathered[0],
+                                       dit.gathered[1], dit.gathered[2], sequence, s.heads,
+                                       s.head_dim, s.scale), attn_flops, repeats)
+    elif world == 1:
+        attn_flops = 4.0 * sequence * sequence * s.heads * s.head_dim
+        out["attention"] = time_kernel(
+            torch, gpu, lambda: gpu.op("sdpa_bf16", dit.attention_heads, dit.query, dit.key,
+                                       dit.value, sequence, s.heads, s.head_dim, s.scale),
+            attn_flops, repeats)
+    return out
+
+
+def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, repeats=10):
+    """The same projections and attention through the reference's CUDA backend (cuBLASLt GEMMs,
+    mma.sync attention; oracle/_ref/libh3ref.so) on the same GPU with the same tensors' contents:
+    name -> ms per launch, CUDA events. Its linears carry no fused epilogue (the norm + RoPE and
+    the SwiGLU are separate kernels there, not timed here), so each figure is a lower bound of
+    what the reference spends on the op this library does in one launch."""
+    if not REF_CUDA.exists():
+        return None
+    s, rows, w = shape, dit.rows_local, step.blocks[0]
+    ref = pkg.Gpu(gpu.device, lib_path=REF_CUDA)
+    try:
+        def copy(tensor, elements):
+            return ref.bf16(tensor.read(elements))
+        x = copy(dit.mod_attention, rows * s.hidden)
+        heads_in = copy(dit.query, rows * s.inner)
+        wide = ref.new(rows * 2 * s.ffn, pkg.BF16)
+        act = copy(dit.qkv, rows * s.ffn)
+        narrow = ref.new(rows * s.hidden, pkg.BF16)
+        weights = {n: copy(getattr(w, n), c) for n, c in
+                   (("qkv", 3 * s.inner * s.hidden), ("out", s.hidden * s.inner),
+                    ("fc1", 2 * s.ffn * s.hidden), ("fc2", s.hidden * s.ffn))}
+        q, k, v = (copy(t, rows * s.inner) for t in (dit.query, dit.key, dit.value))
+        ops = {
+            "qkv_proj_norm_rope": lambda: ref.op("linear_bf16", wide, x, weights["qkv"], None, rows,
+                                                 s.hidden, 3 * s.inner),
+            "mlp_fc1_swiglu": lambda: ref.op("linear_bf16", wide, x, weights["fc1"], None, rows,
+                                             s.hidden, 2 * s.ffn),
+            "mlp_fc2": lambda: ref.op("linear_bf16", narrow, act, weights["fc2"], None, rows, s.ffn,
+                                      s.hidden),
+            "gemm_out_proj": lambda: ref.op("linear_bf16", narrow, heads_in, weights["out"], None,
+                                            rows, s.inner, s.hidden),
+            "attention": lambda: ref.op("sdpa_bf16", heads_in, q, k, v, sequence, s.heads,
+                                        s.head_dim, s.scale),
+        }
+        return {name: time_kernel(torch, ref, fn, 0.0, repeats)[0] for name, fn in ops.items()}
+    except Exception as err:                      # a supplementary figure must not sink the run
+        return {"unavailable": str(err)[:200]}
+    finally:
+        ref.close()
+
+
+PARITY_ROWS, PARITY_TEXT = 1664, 128
+
+
+def parity_vs_single(torch, dist, pkg, gpu, mem, shape, weights, make_exchange, world, rank):
+    """One full-width block (hidden 5376, 56 heads) at S = 1,664 sharded over the ranks, against
+    the same block unsharded on rank 0 (weights are replicated, so rank 0 has everything).
+    Returns {"rel_l2", "max_abs", "ok"} on rank 0 (bar: 1e-2 / 5e-2), None elsewhere."""
+    s, seq = shape, PARITY_ROWS
+    w = weights.blocks[0]
+    rng = np.random.default_rng(7)
+    f = rng.standard_normal(seq * s.hidden, dtype=np.float32).view(np.uint32)
+    hidden = ((f + 0x7fff + ((f >> 16) & 1)) >> 16).astype(np.uint16)
+
+    def run(exchange):
+        dit, step = build_workload(torch, pkg, gpu, mem, s, weights, seq, PARITY_TEXT, exchange)
+        local = np.zeros(dit.rows_local * s.hidden, np.uint16)
+        local[:dit.rows_valid * s.hidden] = hidden[dit.row_begin * s.hidden:
+                                                   (dit.row_begin + dit.rows_valid) * s.hidden]
+        dit.hidden.write(local)
+        gpu.begin()
+        dit.run_block(w, step.row_map, step.rope_cos, step.rope_sin, False, None)
+        gpu.submit()
+        return dit, mem.torch_of(dit.hidden).view(torch.bfloat16)
+
+    exchange = make_exchange()
+    dit, mine = run(exchange)
+    gathered = torch.empty(world * mine.numel(), dtype=torch.bfloat16, device=mine.device)
+    dist.all_gather_into_tensor(gathered, mine.contiguous())
+    result = None
+    if rank == 0:
+        _, single = run(None)
+        a = gathered[:seq * s.hidden].float()
+        b = single[:seq * s.hidden].float()
+        rel = float((a - b).norm() / b.norm())
+        worst = float((a - b).abs().max())
+        result = {"rel_l2": rel, "max_abs": worst, "ok": bool(rel <= 1e-2 and worst <= 5e-2),
+                  "what": f"one full-width block, S={seq}, {s.heads // world} heads and "
+                          f"{dit.rows_local} rows per rank, sharded vs unsharded on rank 0",
+                  "bar": {"rel_l2": 1e-2, "max_abs": 5e-2}}
+    dist.barrier()
+    torch.cuda.synchronize()
+    if hasattr(exchange, "close"):
+        exchange.close()
+    return result
 
 
 def run_gpu_arm(args, shape, sequence, text_rows):
@@ -435,6 +514,7 @@ def run_gpu_arm(args, shape, sequence, text_rows):
     import __graft_entry__ as entry
 
     pkg = entry.load_package()
+    from h3c_b200.plumbing import NcclExchange, TorchMemory
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -446,20 +526,26 @@ def run_gpu_arm(args, shape, sequence, text_rows):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     gpu = pkg.Gpu(local_rank)          # raises if the CUDA library or the device is missing
-    mem = TorchMemory(torch, pkg, gpu, device)
-    exchange = None
-    if world > 1 and args.exchange in ("push", "loopback"):
-        def gather(obj):
-            out = [None] * world
-            dist.all_gather_object(out, obj)
-            return out
-        exchange = pkg.PeerExchange(gpu, world, rank, gather, loopback=args.exchange == "loopback")
-    elif world > 1:
-        exchange = NcclExchange(dist, mem, world, rank)
+    mem = TorchMemory(torch, gpu, device)
     peaks = measured_peaks()
+    s = shape
 
+    def gather(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    def make_exchange():
+        if world == 1:
+            return None
+        if args.exchange in ("push", "loopback"):
+            return pkg.PeerExchange(gpu, world, rank, gather, loopback=args.exchange == "loopback")
+        return NcclExchange(dist, mem, world, rank)
+
+    weights = build_weights(torch, pkg, gpu, mem, shape)
+    exchange = make_exchange()
     try:
-        dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
+        dit, step = build_workload(torch, pkg, gpu, mem, shape, weights, sequence, text_rows, exchange)
     except pkg.H3Error as err:
         # peer mappings (CUDA IPC) are refused on this machine: every rank gets the same error
         # and falls back to the NCCL form of the exchange
@@ -468,40 +554,78 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         if rank == 0:
             print(f"bench: {err}; using pack + NCCL all-to-all + unpack", file=sys.stderr, flush=True)
         args.exchange = "nccl"
-        exchange = NcclExchange(dist, mem, world, rank)
-        dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange)
-    if world > 1 and args.exchange == "loopback":
-        # the slots other ranks would fill must not stay zero: attention's cost and power draw
-        # depend on the data (rescale decisions, switching activity)
-        for t in dit.gathered:
-            mem.torch_of(t).view(torch.bfloat16).normal_(0.0, 1.0)
-    s = shape
-    n_latent = max(1, step.video_rows) * s.video_patch
-    host_latent = torch.randn(n_latent, dtype=torch.float32).pin_memory()
-    host_velocity = torch.empty(n_latent, dtype=torch.bfloat16).pin_memory()
-    latent_t = torch.empty(n_latent, dtype=torch.float32, device=device)
-    velocity_t = torch.empty(n_latent, dtype=torch.bfloat16, device=device)
-    step.latent = gpu.wrap(latent_t.data_ptr(), n_latent, pkg.F32)
-    step.velocity = gpu.wrap(velocity_t.data_ptr(), n_latent, pkg.BF16)
-    latent_t.copy_(host_latent)
+        exchange = make_exchange()
+        dit, step = build_workload(torch, pkg, gpu, mem, shape, weights, sequence, text_rows, exchange)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def one_step():
-        gpu.begin()
-        step.forward()
-        step.euler(-0.05)
-        gpu.submit()          # one synchronisation per evaluated step, as the reference sampler
+    def fill_loopback(d):
+        # the slots other ranks would fill must not stay zero: attention's cost and power draw
+        # depend on the data (rescale decisions, switching activity)
+        if world > 1 and args.exchange == "loopback":
+            for t in d.gathered:
+                mem.torch_of(t).view(torch.bfloat16).normal_(0.0, 1.0)
+
+    def reduce_max(*values):
+        if world == 1:
+            return list(values)
+        t = torch.tensor(values, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t]
+
+    parity = None
+    if world > 1 and args.exchange != "loopback" and not args.no_parity:
+        parity = parity_vs_single(torch, dist, pkg, gpu, mem, shape, weights, make_exchange, world, rank)
+
+    fill_loopback(dit)
+
+    class Latents:
+        """Pinned host latents in, device latents, BF16 velocities out, for one workload."""
+
+        def __init__(self, st):
+            self.n = max(1, st.video_rows) * s.video_patch
+            self.host_latent = torch.randn(self.n, dtype=torch.float32).pin_memory()
+            self.host_velocity = torch.empty(self.n, dtype=torch.bfloat16).pin_memory()
+            self.latent = torch.empty(self.n, dtype=torch.float32, device=device)
+            self.velocity = torch.empty(self.n, dtype=torch.bfloat16, device=device)
+            st.latent = gpu.wrap(self.latent.data_ptr(), self.n, pkg.F32)
+            st.velocity = gpu.wrap(self.velocity.data_ptr(), self.n, pkg.BF16)
+            self.latent.copy_(self.host_latent)
+
+    io = Latents(step)
+    n_latent = io.n
+
+    def stepper(st):
+        def one_step():
+            gpu.begin()
+            st.forward()
+            st.euler(-0.05)
+            gpu.submit()          # one synchronisation per evaluated step, as the reference sampler
+        return one_step
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        return a.elapsed_time(b) / steps
+
+    one_step = stepper(step)
 
     def one_step_e2e():
-        latent_t.copy_(host_latent, non_blocking=True)       # H2D from pinned memory
+        io.latent.copy_(io.host_latent, non_blocking=True)       # H2D from pinned memory
         gpu.begin()
         step.forward()
         gpu.submit()
-        host_velocity.copy_(velocity_t, non_blocking=True)   # D2H of the step's result
+        io.host_velocity.copy_(io.velocity, non_blocking=True)   # D2H of the step's result
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
@@ -511,89 +635,94 @@ def run_gpu_arm(args, shape, sequence, text_rows):
     if rank == 0:
         sampler.start()
     before = gpu.stats()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        one_step()
-    stop.record()
-    barrier()
+    ms_local = timed(one_step, args.steps, 0)
     after = gpu.stats()
     clocks = sampler.stop() if rank == 0 else None
-    ms_local = start.elapsed_time(stop) / args.steps
     launches = ((after.direct_dispatches + after.mps_linear_dispatches + after.mps_sdpa_dispatches) -
                 (before.direct_dispatches + before.mps_linear_dispatches + before.mps_sdpa_dispatches))
 
     # end to end: host buffers in, host buffers out, copies inside the timed region
-    one_step_e2e()
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        one_step_e2e()
-    t1.record()
-    barrier()
-    e2e_local = t0.elapsed_time(t1) / args.steps
-
+    e2e_local = timed(one_step_e2e, args.steps, 1)
+    ms, e2e_ms = reduce_max(ms_local, e2e_local)
+    launches_total = launches
     if world > 1:
-        t = torch.tensor([ms_local, e2e_local], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
-        l = torch.tensor([launches], device=device, dtype=torch.int64)
-        dist.all_reduce(l)
-        launches_total = int(l[0])
-    else:
-        ms, e2e_ms, launches_total = ms_local, e2e_local, launches
+        count = torch.tensor([launches], device=device, dtype=torch.int64)
+        dist.all_reduce(count)
+        launches_total = int(count[0])
+
+    kernels = kernel_timings(torch, pkg, gpu, shape, dit, step, exchange, sequence, world)
+
+    # the second configuration the metric is quoted on, on the same weights: 864x480x121f
+    c4 = None
+    if args.workload == "c3" and not args.no_c4:
+        c4_text, c4_video, c4_desc = WORKLOADS["c4"]
+        c4_seq = c4_text + c4_video
+        ex4 = make_exchange()
+        dit4, step4 = build_workload(torch, pkg, gpu, mem, shape, weights, c4_seq, c4_text, ex4)
+        fill_loopback(dit4)
+        Latents(step4)
+        c4_steps, c4_warmup = 3, 1
+        (c4_ms,) = reduce_max(timed(stepper(step4), c4_steps, c4_warmup))
+        c4_kernels = kernel_timings(torch, pkg, gpu, shape, dit4, step4, ex4, c4_seq, world, repeats=3)
+        c4_tf = s.blocks * s.block_flops(c4_seq) / (c4_ms * 1e-3) / 1e12 / world
+        c4 = {"workload": f"c4: {c4_desc}", "rows": c4_seq, "rows_per_rank": dit4.rows_local,
+              "ms_per_step": c4_ms, "ms_per_block": c4_ms / s.blocks, "steps": c4_steps,
+              "warmup": c4_warmup, "tflops_per_gpu": c4_tf,
+              "frac_of_burst": c4_tf / peaks["bf16_tflops"],
+              "frac_of_sustained": c4_tf / peaks["bf16_tflops_sustained"],
+              "kernels": {k: {"ms": v[0], "tflops": v[1], "frac_of_burst_peak": v[1] / peaks["bf16_tflops"]}
+                          for k, v in c4_kernels.items()}}
+        barrier()
+        if hasattr(ex4, "close"):
+            ex4.close()
 
     line = None
     if rank == 0:
         flops_step = s.blocks * s.block_flops(sequence)
         achieved = flops_step / (ms * 1e-3) / 1e12 / world       # per GPU
-        # live roofline of the dominant kernel (the tensor-core GEMM), timed alone -> burst peak
         rows = dit.rows_local
-        w = step.blocks[0]
-        kernels = {}
-        qkv_flops = 2.0 * rows * s.hidden * 3 * s.inner
-        if dit.push:
-            def qkv_op():
-                gpu.op("h3x_grouped_qkv_linear_rope_push", exchange.peers, dit.mod_attention, w.qkv,
-                       w.q_norm, w.k_norm, step.rope_cos, step.rope_sin, rows, s.hidden, s.heads,
-                       s.head_dim, s.rope_half, s.eps)
-        else:
-            def qkv_op():
-                gpu.op("grouped_qkv_linear_rope_bf16", dit.query, dit.key, dit.value, dit.qkv,
-                       dit.mod_attention, w.qkv, w.q_norm, w.k_norm, step.rope_cos, step.rope_sin,
-                       rows, s.hidden, s.heads, s.head_dim, s.rope_half, s.eps)
-        kernels["qkv_proj_norm_rope"] = time_kernel(torch, gpu, qkv_op, qkv_flops)
-        mlp_flops = 2.0 * rows * s.hidden * 2 * s.ffn + 2.0 * rows * s.ffn * s.hidden
-        kernels["mlp_fc1_swiglu_fc2"] = time_kernel(
-            torch, gpu, lambda: gpu.op("mlp_bf16", dit.attention_output, dit.mod_mlp, w.fc1, w.fc2,
-                                       rows, s.hidden, s.ffn, s.hidden), mlp_flops)
-        out_flops = 2.0 * rows * s.inner * s.hidden
-        kernels["gemm_out_proj"] = time_kernel(
-            torch, gpu, lambda: gpu.op("linear_bf16", dit.attention_output, dit.attention_heads, w.out,
-                                       None, rows, s.inner, s.hidden), out_flops)
-        if dit.push:
-            attn_flops = 4.0 * sequence * sequence * (s.heads // world) * s.head_dim
-            kernels["attention"] = time_kernel(
-                torch, gpu, lambda: gpu.op("h3x_sdpa_push", exchange.peers, dit.gathered[0],
-                                           dit.gathered[1], dit.gathered[2], sequence, s.heads,
-                                           s.head_dim, s.scale), attn_flops)
-        if world == 1:
-            attn_flops = 4.0 * sequence * sequence * s.heads * s.head_dim
-            kernels["attention"] = time_kernel(
-                torch, gpu, lambda: gpu.op("sdpa_bf16", dit.attention_heads, dit.query, dit.key,
-                                           dit.value, sequence, s.heads, s.head_dim, s.scale),
-                attn_flops)
-        qkv_ms, qkv_tf = kernels["qkv_proj_norm_rope"]
+        pair_kernel = 128 < rows <= 8192
+        # the adaLN projection of h3_dit_schedule_precompute at its largest row count: HBM-bound
+        a12_rows = 42
+        mod_cols = s.modalities * s.slots * s.hidden
+        a12_in = mem.bf16(a12_rows * s.time_dim, std=0.125, generator=weights.generator)
+        a12_out = mem.bf16(a12_rows * mod_cols)
+        a12_bytes = 2.0 * (mod_cols * s.time_dim + mod_cols + a12_rows * (s.time_dim + mod_cols))
+        a12_ms, a12_tbs = time_kernel(
+            torch, gpu, lambda: gpu.op("linear_bf16", a12_out, a12_in, weights.proj_w, weights.proj_b,
+                                       a12_rows, s.time_dim, mod_cols), a12_bytes)
+        ref_ops = None
+        if world == 1 and not args.no_reference_cuda:
+            ref_ops = reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence)
+
+        def kernel_entry(name, v):
+            e = {"ms": v[0], "tflops": v[1], "frac_of_burst_peak": v[1] / peaks["bf16_tflops"]}
+            if ref_ops and name in ref_ops:
+                e["reference_cuda_ms"] = ref_ops[name]
+            return e
+        kernel_lines = {k: kernel_entry(k, v) for k, v in kernels.items()}
+        if ref_ops and "unavailable" in ref_ops:
+            kernel_lines["reference_cuda"] = ref_ops
+        kernel_lines["adaln_projection"] = {
+            "ms": a12_ms, "gbs": a12_tbs * 1e3, "frac_of_hbm_peak": a12_tbs * 1e3 / peaks["hbm_gbs"],
+            "bytes_per_launch": a12_bytes, "shape": f"{a12_rows} x {s.time_dim} -> {mod_cols} (+bias)"}
+        fc1_ms, fc1_tf = kernels["mlp_fc1_swiglu"]
+        family = "h3b_gemm_pair" if pair_kernel else "h3b_gemm_tc"
         roofline = {"bound": "tensor",
-                    "kernel": ("h3b_gemm_pair<qkv+norm+rope> (QKV projection with fused head norm and RoPE, CTA pairs)"
-                               if 128 < rows <= 8192 else
-                               "h3b_gemm_tc<qkv+norm+rope> (QKV projection with fused head norm and RoPE)"),
-                    "achieved": qkv_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": qkv_tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst",
-                    "ms_per_launch": qkv_ms, "flops_per_launch": qkv_flops,
+                    "kernel": f"{family}<swiglu> (MLP up projection {s.hidden} -> 2 x {s.ffn} with the "
+                              "SwiGLU epilogue: the launch with the largest share of the step)",
+                    "achieved": fc1_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": fc1_tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst",
+                    "ms_per_launch": fc1_ms, "flops_per_launch": 2.0 * rows * s.hidden * 2 * s.ffn,
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((args.workload, world)),
-                    "traffic_unit": "bytes per launch (dram read+write, one ncu capture)"}
+                    "traffic_unit": "bytes per launch (dram read+write, one ncu capture)",
+                    "traffic_source": NCU_DRAM_SOURCE if (args.workload, world) in NCU_DRAM_BYTES_PER_LAUNCH
+                    else None}
+        if "attention" in kernels:
+            at_ms, at_tf = kernels["attention"]
+            roofline["furthest_from_roof"] = {
+                "kernel": "h3b_sdpa_tc (joint attention)", "achieved": at_tf,
+                "frac": at_tf / peaks["bf16_tflops"], "ms_per_launch": at_ms}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu_ms, desc, threads, _ = cpu_sample(s, sequence)
@@ -611,8 +740,9 @@ def run_gpu_arm(args, shape, sequence, text_rows):
                     "h2d_bytes_per_step": n_latent * 4 * world, "d2h_bytes_per_step": n_latent * 2 * world},
             "gpu_launches": launches_total,
             "roofline": roofline,
-            "kernels": {k: {"ms": v[0], "tflops": v[1], "frac_of_burst_peak": v[1] / peaks["bf16_tflops"]}
-                        for k, v in kernels.items()},
+            "kernels": kernel_lines,
+            "c4": c4,
+            "parity_vs_single": parity,
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
@@ -633,6 +763,8 @@ def run_gpu_arm(args, shape, sequence, text_rows):
     gpu.close()
     if line is not None:
         print(json.dumps(line), flush=True)
+        if parity is not None and not parity["ok"]:
+            raise SystemExit("bench: the sharded block differs from the single-GPU block beyond the parity bar")
 
 
 def run_cfg_arm(args, shape, sequence, text_rows):
@@ -653,7 +785,8 @@ def run_cfg_arm(args, shape, sequence, text_rows):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     gpu = pkg.Gpu(local_rank)
-    mem = TorchMemory(torch, pkg, gpu, device)
+    from h3c_b200.plumbing import NcclPair, TorchMemory
+    mem = TorchMemory(torch, gpu, device)
     euler_steps, guidance = args.euler_steps, args.guidance
     exchange, pair, group_id, half = None, None, 0, 1
     if world > 1:
@@ -668,8 +801,9 @@ def run_cfg_arm(args, shape, sequence, text_rows):
                 return out
             exchange = pkg.PeerExchange(gpu, half, group_rank, gather)
         pair = NcclPair(dist, mem, (rank + half) % world, is_cond=group_id == 0)
-    dit, step = build_model(torch, pkg, gpu, mem, shape, sequence, text_rows, exchange,
-                            time_rows=euler_steps, text_seed=2 if group_id == 0 else 4)
+    weights = build_weights(torch, pkg, gpu, mem, shape, time_rows=euler_steps)
+    dit, step = build_workload(torch, pkg, gpu, mem, shape, weights, sequence, text_rows, exchange,
+                               text_seed=2 if group_id == 0 else 4)
     s = shape
     n_latent = max(1, step.video_rows) * s.video_patch
     noise = torch.Generator()
@@ -765,6 +899,10 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=50)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c4", action="store_true", help="skip the 864x480x121f measurement of the default run")
+    ap.add_argument("--no-parity", action="store_true", help="N>1: skip the sharded-vs-single block check")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="N=1: skip the per-op timing of the reference's CUDA backend")
     ap.add_argument("--exchange", default="push", choices=["push", "nccl", "loopback"],
                     help="N>1: peer stores fused into the kernels, or pack + NCCL all-to-all + unpack; "
                          "loopback = same kernels with the stores kept local and no barriers, to "

@@ -52,7 +52,7 @@ class UlyssesPeers(C.Structure):
 _CTYPES = {
     "void": None, "int": C.c_int, "float": C.c_float, "double": C.c_double,
     "uint32_t": C.c_uint32, "uint64_t": C.c_uint64, "size_t": C.c_size_t,
-    "h3_gpu_dtype": C.c_int,
+    "h3_gpu_dtype": C.c_int, "long long": C.c_longlong,
 }
 
 
@@ -74,6 +74,7 @@ def declared_functions() -> dict[str, tuple]:
     """name -> (restype, [argtypes]) for every function include/h3b200.h declares."""
     text = HEADER.read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"^[ \t]*#.*$", "", text, flags=re.M)          # preprocessor lines
     text = re.sub(r"typedef\s+(struct|enum)\s*\{.*?\}\s*\w+\s*;", "", text, flags=re.S)
     out = {}
     pattern = re.compile(r"([A-Za-z_][\w\s\*]*?)\b(h3x?_\w+|h3b200_\w+)\s*\(([^;{}]*?)\)\s*;", re.S)

@@ -289,6 +289,7 @@ constexpr float AT_RESCALE_THRESHOLD = 8.0f;     /* log2 units */
 struct AttnArgs {
     uint16_t *out;
     int *status;
+    long long wait_cycles;   /* budget of every bounded wait */
     uint32_t seq, heads;
     float scale_log2;
     int head_major;
@@ -298,16 +299,7 @@ struct AttnArgs {
     uint16_t *peer_o[8];
     /* block-sparse mask: per-CTA step lists (see h3_gpu); NULL = dense */
     const uint32_t *sparse_cta_ptr, *sparse_steps;
-    long long *trace;   /* optional [role][tile][event] clock64 stamps of CTA (0,0); NULL = off */
 };
-
-/* Development aid: when args.trace is set, CTA (0,0) records clock64() at the phase
- * boundaries of its first 32 key tiles. */
-#define AT_TRACE(role, j, ev)                                                          \
-    do {                                                                               \
-        if (args.trace && blockIdx.x == 0 && blockIdx.y == 0 && (j) < 32 && lane == 0) \
-            args.trace[((role) * 32 + (j)) * 8 + (ev)] = clock64();                    \
-    } while (0)
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int x, int y, int z) {
@@ -432,13 +424,13 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
             uint32_t ks = 0, kp = 0, vs = 0, vp = 0;
             for (uint32_t j = 0; j < n_tiles; j++) {
                 const int row0 = int((SPARSE ? (steps[j] & 0x0fffffffu) : j) * AT_KV);
-                if (!mbar_wait(k_empty + 8 * ks, kp ^ 1, stop)) break;
+                if (!mbar_wait(k_empty + 8 * ks, kp ^ 1, stop, args.wait_cycles)) break;
                 mbar_expect_tx(k_full + 8 * ks, AT_K_BYTES);
                 tma_load_3d(k_smem + ks * AT_K_BYTES, &map_k, k_full + 8 * ks, 0, int(head), row0);
                 tma_load_3d(k_smem + ks * AT_K_BYTES + AT_K_BYTES / 2, &map_k, k_full + 8 * ks, 64,
                             int(head), row0);
                 if (++ks == AT_K_STAGES) { ks = 0; kp ^= 1; }
-                if (!mbar_wait(v_empty + 8 * vs, vp ^ 1, stop)) break;
+                if (!mbar_wait(v_empty + 8 * vs, vp ^ 1, stop, args.wait_cycles)) break;
                 mbar_expect_tx(v_full + 8 * vs, AT_V_BYTES);
                 tma_load_3d(v_smem + vs * AT_V_BYTES, &map_v, v_full + 8 * vs, 0, int(head), row0);
                 tma_load_3d(v_smem + vs * AT_V_BYTES + AT_V_BYTES / 2, &map_v, v_full + 8 * vs, 64,
@@ -469,7 +461,7 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                                   leader);
                 umma_commit_if(s_full + 8 * t, leader);
             };
-            bool alive = mbar_wait(q_full, 0, stop) && mbar_wait(k_full, 0, stop);
+            bool alive = mbar_wait(q_full, 0, stop, args.wait_cycles) && mbar_wait(k_full, 0, stop, args.wait_cycles);
             alive = __all_sync(0xffffffffu, alive);
             if (alive) {
                 tc_fence_after();
@@ -482,7 +474,6 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 const uint32_t v_lo = v_lo0 + vs * (AT_V_BYTES >> 4);
                 const uint32_t k_lo_next = k_lo0 + ks * (AT_K_BYTES >> 4);
                 const bool more = j + 1 < n_tiles;
-                AT_TRACE(0, j, 0);
 #pragma unroll
                 for (int t = 0; t < AT_TILES; t++) {
                     /* P_t arrives in two parts: each softmax warp publishes the first 32 of its
@@ -492,14 +483,13 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                      * come first: a wait in the middle of a run of MMAs lets the short queue of
                      * the tensor pipe run dry, even when the barrier has already flipped. */
                     if (t == 0) {
-                        alive = mbar_wait(v_full + 8 * vs, vp, stop);
-                        if (alive && more) alive = mbar_wait(k_full + 8 * ks, kp, stop);
+                        alive = mbar_wait(v_full + 8 * vs, vp, stop, args.wait_cycles);
+                        if (alive && more) alive = mbar_wait(k_full + 8 * ks, kp, stop, args.wait_cycles);
                     }
-                    alive = __all_sync(0xffffffffu, alive && mbar_wait(p_full + 16 * t, j & 1, stop));
+                    alive = __all_sync(0xffffffffu, alive && mbar_wait(p_full + 16 * t, j & 1, stop, args.wait_cycles));
                     if (!alive) break;
                     /* the second part of P_t is usually complete by now: one fence, eight MMAs */
                     const bool late_ready = __all_sync(0xffffffffu, mbar_try(p_full + 16 * t + 8, j & 1));
-                    AT_TRACE(0, j, 1 + 2 * t);
                     tc_fence_after();
                     /* O_t += P_t . V_j : A = P_t in TMEM (first 64 columns of S_t), 8 columns and
                      * 2048 bytes of V per 16 keys */
@@ -511,7 +501,7 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                     umma_ts<true>(d, a + 4 * 8, v_lo + 4 * (2048 >> 4), idesc_pv, leader);
                     umma_ts<true>(d, a + 5 * 8, v_lo + 5 * (2048 >> 4), idesc_pv, leader);
                     if (!late_ready) {
-                        alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t + 8, j & 1, stop));
+                        alive = __all_sync(0xffffffffu, mbar_wait(p_full + 16 * t + 8, j & 1, stop, args.wait_cycles));
                         if (!alive) break;
                         tc_fence_after();
                     }
@@ -526,7 +516,6 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                         issue_qk(t, k_lo_next);
                         if (t == AT_TILES - 1) umma_commit_if(k_empty + 8 * ks, leader);
                     }
-                    AT_TRACE(0, j, 2 + 2 * t);
                 }
                 if (!alive) break;
                 if (++vs == AT_V_STAGES) { vs = 0; vp ^= 1; }
@@ -558,10 +547,8 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         float m_run = -INFINITY, l_run = 0.0f;
         bool alive = true;
         for (uint32_t j = 0; alive && j < n_tiles; j++) {
-            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 0);
             /* S_t(j) complete; every earlier MMA of this CTA (P.V of tile j-1 included) too */
-            const bool ready = __all_sync(0xffffffffu, mbar_wait(my_s_full, j & 1, stop));
-            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 1);
+            const bool ready = __all_sync(0xffffffffu, mbar_wait(my_s_full, j & 1, stop, args.wait_cycles));
             tc_fence_after();
             /* the loads run even if the wait gave up (tensor-memory reads are always safe), so
              * the score registers have one definition and stay in registers */
@@ -609,7 +596,6 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 if (!both) { alive = false; break; }
             }
             const float m_tile = fmaxf(mx_half, *theirs) * scale_log2;
-            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 2);
             float alpha = 1.0f;
             bool rescale = false;
             if (m_tile - m_run > AT_RESCALE_THRESHOLD) {   /* also true on the first tile */
@@ -668,13 +654,11 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(my_p_full + 8 * part);
-                if (part == 0 && quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 3);
             }
             float sum0, sum1, sum2, sum3;
             unpack_f32x2(sum_a, sum0, sum1);
             unpack_f32x2(sum_b, sum2, sum3);
             l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
-            if (quarter == 0 && half == 0) AT_TRACE(1 + tile, j, 4);
         }
         /* total row sum = sum of the two halves' partial sums (same reference maximum) */
         if (alive) *mine = l_run;
@@ -684,11 +668,14 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
          * normalised output there (16-byte chunks, chunk index XOR row: no bank conflicts on
          * either side) and then write whole 256-byte rows, two rows per store instruction.
          * Full-line stores matter when the destination is another GPU's memory. */
-        const bool finished = alive && mbar_wait(o_done, 0, stop);
+        const bool finished = alive && mbar_wait(o_done, 0, stop, args.wait_cycles);
         const uint32_t stage = q_smem + (tile * 4 + quarter) * 8192;
         if (finished) {
             tc_fence_after();
-            const float inv = 1.0f / (l_run + *theirs);
+            /* a row whose keys are all masked has sum 0 and O = 0: it gets zeros, as in the
+             * reference (h3_cuda_attention.cu:1790,1800), not 0 * inf */
+            const float l_row = l_run + *theirs;
+            const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
 #pragma unroll 1
             for (uint32_t c = 0; c < 2; c++) {
                 uint32_t o[32];
@@ -803,6 +790,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         return h3b_fail(gpu, "the block-sparse mask needs head_dim 128, aligned tensors and the tensor-core kernel");
     if (hd == AT_D && aligned && !simt && scale > 0.0f) {
         static bool configured_on[64];      /* the attribute is per device */
+        static std::mutex configure_mutex;
+        std::unique_lock<std::mutex> configure_guard(configure_mutex);
         bool &configured = configured_on[gpu->device & 63];
         if (!configured) {
             bool ok = true;
@@ -816,6 +805,7 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
             }
             configured = true;
         }
+        configure_guard.unlock();
         CUtensorMap map_q, map_k, map_v;
         if (!make_qkv_map(&map_q, h3b_ptr<uint16_t>(query), seq, heads, AT_Q) ||
             !make_qkv_map(&map_k, h3b_ptr<uint16_t>(key), seq, heads, AT_KV) ||
@@ -836,12 +826,11 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
             args.sparse_steps = gpu->sparse_steps;
         }
         args.status = gpu->status_device;
+        args.wait_cycles = gpu->wait_cycles;
         args.seq = seq;
         args.heads = heads;
         args.scale_log2 = scale * 1.4426950408889634f;
         args.head_major = head_major;
-        args.trace = nullptr;
-        if (const char *t = getenv("H3B_ATTN_TRACE_PTR")) args.trace = reinterpret_cast<long long *>(strtoull(t, nullptr, 0));
         dim3 grid((seq + AT_Q - 1) / AT_Q, heads);
         auto *kernel = peers ? (sparse ? h3b_sdpa_tc<true, true> : h3b_sdpa_tc<true, false>)
                              : (sparse ? h3b_sdpa_tc<false, true> : h3b_sdpa_tc<false, false>);

@@ -66,6 +66,11 @@ struct h3_gpu {
 
     int *status_device = nullptr;   /* kernel status word */
     int status_seen = 0;
+    /* budgets of the bounded device-side waits, in SM clock cycles (h3x_set_wait_budget_cycles):
+     * pipeline waits inside the GEMM and attention kernels (~1 s), and the cross-rank barrier,
+     * which also has to absorb the skew between ranks (~10 s) */
+    long long wait_cycles = 2000000000ll;
+    long long barrier_cycles = 20000000000ll;
 
     /* Block-sparse attention mask (h3_gpu_sdpa_set_sparse), regrouped for the tensor-core
      * kernel: one list per CTA (256 query rows = two 128-row query blocks) of steps over
@@ -77,7 +82,6 @@ struct h3_gpu {
 
     char profile_label[128] = {0};
     double profile_mark = 0.0;
-    std::mutex io_mutex;            /* file streaming may run on another thread */
 };
 
 double h3b_now();

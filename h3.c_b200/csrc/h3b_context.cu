@@ -225,6 +225,15 @@ extern "C" int h3x_kernel_status(h3_gpu *gpu) {
     return status;
 }
 
+extern "C" int h3x_set_wait_budget_cycles(h3_gpu *gpu, long long kernel_cycles,
+                                          long long barrier_cycles) {
+    if (!gpu) return 0;
+    if (gpu->active) return h3b_fail(gpu, "cannot change the wait budget inside a command");
+    if (kernel_cycles > 0) gpu->wait_cycles = kernel_cycles;
+    if (barrier_cycles > 0) gpu->barrier_cycles = barrier_cycles;
+    return 1;
+}
+
 extern "C" int h3_gpu_begin(h3_gpu *gpu) {
     if (!gpu || gpu->active) return 0;
     gpu->error[0] = '\0';
@@ -501,10 +510,15 @@ extern "C" int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *t, size_t o, const 
 /* Payload bytes are read with pread() into a pinned bounce buffer, 16 MiB at a
  * time on two alternating buffers, and copied to the device on a private
  * stream, so a load may run on an I/O thread while the main thread keeps
- * issuing kernels on tensors that are not being filled. */
+ * issuing kernels on tensors that are not being filled.
+ * after_context: the first copy waits (on the device, through an event) for the work queued
+ * on the context's stream at the time of the call, so kernels that still read the tensor's
+ * previous contents finish first. The streaming entry point does not wait: its contract is a
+ * target that is idle on the context's stream, so that the upload overlaps the running block. */
 
 static int fill_from_file(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
-                          size_t elements, h3_gpu_dtype dtype, char *error, size_t error_size) {
+                          size_t elements, h3_gpu_dtype dtype, char *error, size_t error_size,
+                          bool after_context = false) {
     auto fail = [&](const char *what) {
         if (error && error_size) snprintf(error, error_size, "%s: %s", what, path ? path : "(null)");
         return 0;
@@ -527,6 +541,14 @@ static int fill_from_file(h3_gpu_tensor *tensor, const char *path, uint64_t file
             cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) != cudaSuccess)
             ok = 0;
     if (!ok) fail("cannot allocate staging memory for");
+    if (ok && gpu && after_context) {
+        cudaEvent_t queued = nullptr;
+        if (cudaEventCreateWithFlags(&queued, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventRecord(queued, gpu->stream) != cudaSuccess ||
+            cudaStreamWaitEvent(stream, queued, 0) != cudaSuccess)
+            ok = fail("cannot order the upload after the context's stream for");
+        if (queued) cudaEventDestroy(queued);
+    }
     size_t moved = 0;
     for (int turn = 0; ok && moved < bytes; turn ^= 1) {
         size_t want = bytes - moved < chunk ? bytes - moved : chunk;
@@ -585,7 +607,7 @@ extern "C" h3_gpu_tensor *h3_gpu_tensor_load_f32(h3_gpu *gpu, const char *path, 
 extern "C" int h3_gpu_tensor_read_file_bf16(h3_gpu_tensor *tensor, const char *path,
                                             uint64_t offset, size_t elements, char *error,
                                             size_t error_size) {
-    return fill_from_file(tensor, path, offset, elements, H3_GPU_BF16, error, error_size);
+    return fill_from_file(tensor, path, offset, elements, H3_GPU_BF16, error, error_size, true);
 }
 extern "C" int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *tensor, const char *path,
                                               uint64_t offset, size_t elements, char *error,
@@ -673,6 +695,34 @@ extern "C" int h3_gpu_copy_bf16(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offs
 extern "C" int h3_gpu_copy_f32(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offset,
                                const h3_gpu_tensor *src, size_t src_offset, size_t elements) {
     return device_copy(gpu, dst, dst_offset, src, src_offset, elements, H3_GPU_F32);
+}
+
+extern "C" int h3_cuda_probe(h3_device_info *info, char *error, size_t error_size) {
+    if (!info) return 0;
+    memset(info, 0, sizeof(*info));
+    int count = 0;
+    cudaError_t status = cudaGetDeviceCount(&count);
+    if (status != cudaSuccess || count < 1) {
+        if (error && error_size)
+            snprintf(error, error_size, "no CUDA device available: %s", cudaGetErrorString(status));
+        cudaGetLastError();
+        return 0;
+    }
+    cudaDeviceProp prop;
+    status = cudaGetDeviceProperties(&prop, g_device);
+    if (status != cudaSuccess) {
+        if (error && error_size)
+            snprintf(error, error_size, "cannot query CUDA device: %s", cudaGetErrorString(status));
+        cudaGetLastError();
+        return 0;
+    }
+    snprintf(info->name, sizeof(info->name), "%.127s", prop.name);
+    snprintf(info->architecture, sizeof(info->architecture), "sm_%d%d", prop.major, prop.minor);
+    const long pages = sysconf(_SC_PHYS_PAGES), page_size = sysconf(_SC_PAGESIZE);
+    if (pages > 0 && page_size > 0) info->physical_memory = uint64_t(pages) * uint64_t(page_size);
+    info->recommended_working_set = prop.totalGlobalMem;
+    info->max_buffer_length = prop.totalGlobalMem;
+    return 1;
 }
 
 extern "C" int h3b200_probe(h3b200_device_info *info, char *error, size_t error_size) {

@@ -62,6 +62,7 @@ struct TcArgs {
     uint16_t *out;
     const uint16_t *bias;
     int *status;
+    long long wait_cycles; /* budget of every bounded wait */
     uint32_t rows;        /* M */
     uint32_t out_cols;    /* stored columns (n, or hidden for SwiGLU) */
     uint32_t k_blocks;
@@ -314,7 +315,7 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 uint32_t m_blk, n_blk;
                 tile_coords(tile, m_blk, n_blk);
                 for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
-                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop)) { alive = false; break; }
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop, args.wait_cycles)) { alive = false; break; }
                     uint32_t bar = full_bar + 8 * stage;
                     mbar_expect_tx(bar, A_BYTES + B_BYTES);
                     tma_load_2d(a_smem + stage * A_BYTES, &map_a, bar, int(kb * BK), int(m_blk * BM));
@@ -343,11 +344,11 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
             for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
-                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop))) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop, args.wait_cycles))) break;
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + acc * BN;
                 for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop))) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop, args.wait_cycles))) {
                         alive = false;
                         break;
                     }
@@ -375,7 +376,7 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t m_blk, n_blk;
             tile_coords(tile, m_blk, n_blk);
-            if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop)) break;
+            if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop, args.wait_cycles)) break;
             tc_fence_after();
             const uint32_t row = m_blk * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
@@ -490,7 +491,7 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                                       ? int((rank ? args.up_offset : 0u) + n_blk * 128)
                                       : int(n_blk * BN + rank * 128);
                 for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
-                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop)) { alive = false; break; }
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop, args.wait_cycles)) { alive = false; break; }
                     const uint32_t bar = cluster_map(full_bar + 8 * stage, 0);
                     if (rank == 0) mbar_expect_tx(full_bar + 8 * stage, 2 * PAIR_STAGE_BYTES);
                     tma_load_2d_pair(a_smem + stage * A_BYTES, &map_a, bar, int(kb * BK), a_row);
@@ -508,11 +509,11 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
             for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
-                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop))) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop, args.wait_cycles))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop))) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop, args.wait_cycles))) {
                         alive = false;
                         break;
                     }
@@ -539,7 +540,7 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
             uint32_t m_blk, n_blk;
             tile_coords(tile, m_blk, n_blk);
-            if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop)) break;
+            if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop, args.wait_cycles)) break;
             tc_fence_after();
             const uint32_t row = m_blk * 256 + rank * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
@@ -675,6 +676,8 @@ int max_resident_pairs(int device) {
     /* function attributes and occupancy belong to a device: one answer per device */
     static int per_device[64];
     static bool known[64];
+    static std::mutex guard_mutex;      /* contexts on several threads may launch their first GEMM together */
+    std::lock_guard<std::mutex> guard(guard_mutex);
     int &pairs = per_device[device & 63];
     if (known[device & 63]) return pairs;
     known[device & 63] = true;
@@ -701,7 +704,6 @@ int max_resident_pairs(int device) {
         return pairs;
     }
     pairs = clusters;
-    if (env_flag("H3B_REPORT_PAIRS")) fprintf(stderr, "h3b200: %d resident CTA pairs for epilogue %d\n", pairs, EPI);
     return pairs;
 }
 
@@ -711,8 +713,10 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               uint32_t out_cols, uint32_t tiles_n, uint32_t up_offset,
               const TcArgs *extra = nullptr) {
     static bool configured_on[64];      /* the attribute is per device */
-    bool &configured = configured_on[gpu->device & 63];
+    static std::mutex configure_mutex;
     constexpr size_t smem_bytes = EPI == H3B_EPI_QKV_ROPE ? TC_SMEM_QKV : TC_SMEM;
+    std::unique_lock<std::mutex> configure_guard(configure_mutex);
+    bool &configured = configured_on[gpu->device & 63];
     if (!configured) {
         if (cudaFuncSetAttribute(h3b_gemm_tc<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(smem_bytes)) != cudaSuccess) {
@@ -721,6 +725,7 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
         }
         configured = true;
     }
+    configure_guard.unlock();
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, x, rows, k, BM) || !make_map(&map_b, w, weight_rows, k, 128)) return 0;
     TcArgs args = {};
@@ -728,6 +733,7 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
     args.out = out;
     args.bias = bias;
     args.status = gpu->status_device;
+    args.wait_cycles = gpu->wait_cycles;
     args.rows = rows;
     args.out_cols = out_cols;
     args.k_blocks = (k + BK - 1) / BK;
@@ -933,6 +939,21 @@ extern "C" int h3_gpu_mlp_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
     gpu->stats.mps_linear_dispatches = linear_before + 2;
     gpu->stats.direct_dispatches = direct_before;
     return 1;
+}
+
+/* The first stage of h3_gpu_mlp_bf16 on its own: activated = swiglu(x . fc1^T). */
+extern "C" int h3x_linear_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                                      const h3_gpu_tensor *fc1_weight, uint32_t rows,
+                                      uint32_t input_dim, uint32_t hidden_dim) {
+    if (!h3b_need(gpu, input, H3_GPU_BF16, size_t(rows) * input_dim, "MLP input") ||
+        !h3b_need(gpu, fc1_weight, H3_GPU_BF16, size_t(hidden_dim) * 2 * input_dim, "MLP fc1") ||
+        !h3b_need(gpu, output, H3_GPU_BF16, size_t(rows) * hidden_dim, "MLP activation") ||
+        !h3b_need_command(gpu))
+        return 0;
+    if (!rows || !hidden_dim) return 1;
+    return h3b_gemm_bf16(gpu, h3b_ptr<uint16_t>(output), h3b_ptr<uint16_t>(input),
+                         h3b_ptr<uint16_t>(fc1_weight), nullptr, rows, input_dim, hidden_dim,
+                         H3B_EPI_SWIGLU, "linear_swiglu_bf16");
 }
 
 static int patch_common(h3_gpu *gpu, h3_gpu_tensor *output, size_t output_offset,

@@ -92,7 +92,7 @@ extern "C" int h3x_peer_barrier(h3_gpu *gpu, const h3x_ulysses_peers *peers) {
         if (!peers->flags[r]) return h3b_fail(gpu, "peer table has no barrier words");
     if (!h3b_need_command(gpu)) return 0;
     h3b_peer_barrier<<<1, 32, 0, gpu->stream>>>(static_cast<uint32_t *>(peers->flags[peers->rank]),
-                                                *peers, gpu->status_device, 20000000000ll);
+                                                *peers, gpu->status_device, gpu->barrier_cycles);
     return h3b_launched(gpu, "peer_barrier");
 }
 

@@ -729,11 +729,19 @@ static uint16_t *noalloc_scratch_for(h3_gpu *gpu) {
         h3b_fail_cuda(gpu, "cudaGetDevice", status);
         return nullptr;
     }
-    if (current != gpu->device || current < 0 || current >= kNoAllocMaxDevices) {
+    if (current < 0 || current >= kNoAllocMaxDevices) {
+        h3b_fail(gpu, "h3x_adaln_linear_bf16_noalloc serves device indices 0..%d; the current device is %d",
+                 kNoAllocMaxDevices - 1, current);
+        return nullptr;
+    }
+    if (current != gpu->device) {
         h3b_fail(gpu, "the context's device %d is not the calling thread's current device %d",
                  gpu->device, current);
         return nullptr;
     }
+    /* threads of different contexts may make their first call on a device at the same time */
+    static std::mutex lookup;
+    std::lock_guard<std::mutex> guard(lookup);
     if (!g_noalloc_scratch_address[current]) {
         void *address = nullptr;
         status = cudaGetSymbolAddress(&address, g_noalloc_scratch);

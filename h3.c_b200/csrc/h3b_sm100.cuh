@@ -42,17 +42,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-constexpr long long kWaitCycles = 2000000000ll; /* ~1 s at 2 GHz */
-
-/* Bounded wait. Returns false when the CTA should stop. */
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *stop) {
+/* Bounded wait: gives up after `limit` cycles of the SM clock without progress (the context's
+ * wait budget, about a second by default). Returns false when the CTA should stop. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *stop,
+                                          long long limit) {
     if (mbar_try(bar, parity)) return true;
     long long start = clock64();
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try(bar, parity)) return true;
         if ((spin & 255u) == 0) {
             if (*stop) return false;
-            if (clock64() - start > kWaitCycles) {
+            if (clock64() - start > limit) {
                 *stop = 1;
                 return false;
             }

@@ -86,6 +86,13 @@ h3_gpu_tensor *h3_gpu_tensor_load_bf16(h3_gpu *gpu, const char *path, uint64_t f
                                        size_t elements);
 h3_gpu_tensor *h3_gpu_tensor_load_f32(h3_gpu *gpu, const char *path, uint64_t file_offset,
                                       size_t elements);
+/* Both fill an existing tensor from a file on a private copy stream and return when the data
+ * is on the device; they may run on an I/O thread while the context's thread issues kernels on
+ * other tensors (h3_gpu.h:66-78). read_file orders its first copy after the work already queued
+ * on the context's stream, so kernels that still read the old contents finish first.
+ * stream_file does not wait (it is the double-buffer path that must overlap the running block,
+ * h3_dit.c:2355-2433): its target must be idle on the context's stream when it is called.
+ * Either way, work on a stream other than the context's is the caller's to order. */
 int h3_gpu_tensor_read_file_bf16(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
                                  size_t elements, char *error, size_t error_size);
 int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
@@ -273,7 +280,26 @@ int h3_gpu_token_expand_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *residual, h3_gpu_
                                    uint32_t exact_prefix_rows, float update_scale, uint32_t slots,
                                    uint32_t shift_slot, uint32_t scale_slot, float epsilon);
 
-/* ---- device probe: h3_cuda.h:9; h3_gpu_cuda.cu:1032-1046 ----------------- */
+/* ---- device probe: h3_cuda.h:9; h3_gpu_cuda.cu:47-79 ----------------------
+ * h3_cuda_probe is what the reference's pipeline calls (h3.c:465, tests/test_h3.c:385); its
+ * struct belongs to the pipeline header h3.h (guard H3_H, h3.h:132-146), so it is declared
+ * here with the same layout only when that header was not included first. Fields as the
+ * reference fills them: device name, "sm_XY", host RAM, device memory twice, and zeros for
+ * the three Apple-only fields. */
+#ifndef H3_H
+typedef struct {
+    char name[128];
+    char architecture[128];
+    uint64_t physical_memory;
+    uint64_t recommended_working_set;
+    uint64_t max_buffer_length;
+    int apple_gpu_family;
+    int metal4;
+    int unified_memory;
+} h3_device_info;
+#endif
+int h3_cuda_probe(h3_device_info *info, char *error, size_t error_size);
+/* The same probe with the fields a CUDA host wants (SM count, compute capability). */
 typedef struct {
     char name[256];
     uint64_t total_memory;
@@ -300,6 +326,13 @@ h3_gpu_tensor *h3x_tensor_wrap(h3_gpu *gpu, void *device_pointer, size_t element
 void *h3x_tensor_device_pointer(const h3_gpu_tensor *tensor);
 /* Last asynchronous kernel status word (0 = ok), read after h3_gpu_submit(). */
 int h3x_kernel_status(h3_gpu *gpu);
+/* Every device-side wait is bounded: a kernel that sees no progress for its budget records a
+ * status, returns normally, and the next h3_gpu_submit() fails with a message (the context
+ * stays usable and the status word is cleared). Budgets are in SM clock cycles; a value <= 0
+ * keeps the current one. kernel_cycles bounds the pipeline waits inside the GEMM and attention
+ * kernels (default 2e9, about a second); barrier_cycles bounds h3x_peer_barrier, which also
+ * absorbs the skew between ranks (default 2e10). Not allowed inside a command. */
+int h3x_set_wait_budget_cycles(h3_gpu *gpu, long long kernel_cycles, long long barrier_cycles);
 
 /* Ulysses exchange layout. `packed` holds, for each of `world` peers p, the
  * contiguous block [rows_local][heads/world][head_dim] of heads
@@ -345,7 +378,8 @@ int h3x_sdpa_push(h3_gpu *gpu, const h3x_ulysses_peers *peers, const h3_gpu_tens
 /* Barrier across the ranks on this context's stream: one small kernel that raises this rank's
  * epoch in every peer's flag words (release, system scope) and waits until every peer's epoch
  * arrived in its own. Each rank must run on its own GPU. The wait is bounded (about 10 s of
- * GPU clock); when it runs out the kernel status word becomes non-zero and submit fails. */
+ * GPU clock unless h3x_set_wait_budget_cycles changed it); when it runs out the kernel status
+ * word becomes non-zero and submit fails. */
 int h3x_peer_barrier(h3_gpu *gpu, const h3x_ulysses_peers *peers);
 /* Device memory that other processes on the node can map (CUDA IPC). alloc returns a zeroed
  * cudaMalloc block and fills the 64-byte handle to send to the peers; open maps a peer's block
@@ -360,6 +394,15 @@ int h3x_peer_free(h3_gpu *gpu, void *block);
  * multiply-add of the F32 difference. out may alias either input. */
 int h3x_cfg_combine_bf16(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_tensor *cond,
                          const h3_gpu_tensor *uncond, uint32_t elements, float guidance);
+
+/* The MLP's up projection with its activation, as one op (the first stage of h3_gpu_mlp_bf16,
+ * h3_cuda_core.cu:1050-1110, exposed so that a host can time it or keep the activation):
+ * fused = bf16(input . fc1^T) with fc1 = [gate rows | up rows] of hidden_dim each, then
+ * output[r][c] = bf16(silu(fused[r][c]) * fused[r][hidden_dim + c]); output is [rows][hidden_dim].
+ * Counted as one projection. */
+int h3x_linear_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                           const h3_gpu_tensor *fc1_weight, uint32_t rows, uint32_t input_dim,
+                           uint32_t hidden_dim);
 
 /* Final head (adaLN + projection) for callers that must not allocate device memory.
  * No counterpart in the reference: its final head always draws its scratch from a

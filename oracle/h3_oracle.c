@@ -15,6 +15,14 @@
 #include <omp.h>
 #endif
 
+void h3o_set_threads(int count) {
+#ifdef _OPENMP
+    if (count > 0) omp_set_num_threads(count);
+#else
+    (void)count;
+#endif
+}
+
 int h3o_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -520,12 +528,14 @@ static void sdpa_core(uint16_t *out, const uint16_t *q, const uint16_t *k,
                     scores[j] = scores[j] * scale;
                     if (scores[j] > mx) mx = scores[j];
                 }
+                /* a row whose block lists no tile attends nothing: probabilities and sum are 0
+                 * and the row is written as zeros (h3_cuda_attention.cu:1790,1800) */
                 float sum = 0.0f;
                 for (uint32_t j = 0; j < seq; j++) {
-                    scores[j] = expf(scores[j] - mx);
+                    scores[j] = mx == -INFINITY ? 0.0f : expf(scores[j] - mx);
                     sum += scores[j];
                 }
-                float inv = 1.0f / sum;
+                float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
                 for (uint32_t d = 0; d < hd; d++) acc[d] = 0.0f;
                 for (uint32_t j = 0; j < seq; j++) {
                     float p = round_p ? bf_round(scores[j]) : scores[j] * inv;

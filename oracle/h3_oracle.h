@@ -202,6 +202,8 @@ void h3o_dit_block(uint16_t *hidden, const h3o_block_weights *w,
                    uint16_t *dump_attention_output, uint16_t *dump_mod_mlp);
 
 int h3o_threads(void);
+/* OpenMP threads used from now on (a launcher may have exported OMP_NUM_THREADS=1) */
+void h3o_set_threads(int count);
 
 #ifdef __cplusplus
 }

@@ -58,6 +58,11 @@ def threads() -> int:
     return lib().h3o_threads()
 
 
+def set_threads(count: int) -> None:
+    """Use `count` OpenMP threads from now on (torch.distributed.run exports OMP_NUM_THREADS=1)."""
+    lib().h3o_set_threads(int(count))
+
+
 # ----------------------------------------------------------------- bf16
 def to_bf16(x: np.ndarray) -> np.ndarray:
     """F32 -> raw BF16 bits, round to nearest even (reference formula)."""

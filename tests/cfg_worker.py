@@ -18,9 +18,11 @@ ROOT = Path(__file__).resolve().parent.parent
 for p in (ROOT, ROOT / "oracle", ROOT / "tests"):
     sys.path.insert(0, str(p))
 
-from bench import NcclPair, TorchMemory  # noqa: E402
 from denoise_case import PATCH, cosine, gpu_denoise, make_denoise_case, oracle_denoise  # noqa: E402
 import __graft_entry__ as entry  # noqa: E402
+
+entry.load_package()
+from h3c_b200.plumbing import NcclPair, TorchMemory  # noqa: E402
 
 
 def main():
@@ -34,7 +36,7 @@ def main():
     group_id, group_rank = rank // half, rank % half
     groups = [dist.new_group(list(range(g * half, (g + 1) * half))) for g in range(2)]
     gpu = pkg.Gpu(local)
-    mem = TorchMemory(torch, pkg, gpu, device)
+    mem = TorchMemory(torch, gpu, device)
     guidance = 3.0
     case = make_denoise_case(rows=203, text_rows=40, blocks=2, steps=3, seed=9,
                              sigmas=pkg.serving_sigmas(3))

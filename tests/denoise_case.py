@@ -54,14 +54,21 @@ class DenoiseCase:
 
 
 def make_denoise_case(rows=200, text_rows=40, heads=4, hidden=5376, ffn=1024, blocks=2, steps=4,
-                      seed=0, fast=False, sigmas=None) -> DenoiseCase:
+                      seed=0, fast=False, sigmas=None, distinct=None) -> DenoiseCase:
+    """distinct: number of different sets of projection weights; block b uses set b % distinct
+    (the arrays are shared, and uploaded once), while every block keeps its own modulation
+    table. Deep cases (50 blocks) then cost a few GB instead of 38."""
     c = DenoiseCase(rows, text_rows, heads, hidden, ffn, steps)
     inner = heads * 128
     one = o.to_bf16(np.ones(1, np.float32))[0]
+    distinct = blocks if distinct is None else min(distinct, blocks)
     for b in range(blocks):
         w = {}
         for name, count in (("qkv_weight", 3 * inner * hidden), ("out_weight", hidden * inner),
                             ("fc1_weight", 2 * ffn * hidden), ("fc2_weight", hidden * ffn)):
+            if b >= distinct:
+                w[name] = c.blocks[b % distinct][name]
+                continue
             w[name] = _normal_bf16(count, o.named_seed(seed, f"blocks.{b}.{name}"), 0.02, fast)
         w["norm1"] = np.full(hidden, one, np.uint16)
         w["norm2"] = np.full(hidden, one, np.uint16)
@@ -143,7 +150,13 @@ def gpu_denoise(pkg, gpu, c: DenoiseCase, *, guidance=None, exchange=None, pair=
     shape = pkg.DitShape(hidden=c.hidden_dim, heads=c.heads, ffn=c.ffn, blocks=len(c.blocks))
     dit = pkg.Dit(gpu, shape, c.rows, exchange=exchange, alloc=alloc)
     r0, rl, valid = dit.row_begin, dit.rows_local, dit.rows_valid
-    blocks = [pkg.BlockWeights(**{drv: gpu.bf16(w[orc]) for orc, drv in ORACLE_TO_DRIVER.items()})
+    uploaded = {}
+
+    def upload_once(array):      # blocks of a deep case share their projection weights
+        if id(array) not in uploaded:
+            uploaded[id(array)] = gpu.bf16(array)
+        return uploaded[id(array)]
+    blocks = [pkg.BlockWeights(**{drv: upload_once(w[orc]) for orc, drv in ORACLE_TO_DRIVER.items()})
               for w in c.blocks]
 
     def rows_of(a, width, dtype, lo=r0, n=valid, pad=rl):

@@ -158,3 +158,54 @@ def test_entry_points_off_the_dit_path_fail_with_a_message(gpu, pkg):
     gpu.submit()
     assert lib.h3_gpu_is_m5(gpu.handle) == 0 and lib.h3_gpu_has_int8_mlp(gpu.handle) == 0
     assert lib.h3_gpu_prefers_gpu_sampler(gpu.handle) == 1
+
+
+def test_cuda_probe_fills_the_reference_struct(gpu, pkg):
+    """h3_cuda_probe (h3_cuda.h:9, h3_gpu_cuda.cu:47-79) with the h3_device_info layout of
+    h3.h:132-146: name, "sm_XY", host RAM, device memory twice, zeros for the Apple-only fields."""
+    class DeviceInfo(C.Structure):
+        _fields_ = [("name", C.c_char * 128), ("architecture", C.c_char * 128),
+                    ("physical_memory", C.c_uint64), ("recommended_working_set", C.c_uint64),
+                    ("max_buffer_length", C.c_uint64), ("apple_gpu_family", C.c_int),
+                    ("metal4", C.c_int), ("unified_memory", C.c_int)]
+    info, err = DeviceInfo(), C.create_string_buffer(256)
+    fn = gpu.lib.h3_cuda_probe
+    fn.restype, fn.argtypes = C.c_int, [C.POINTER(DeviceInfo), C.c_char_p, C.c_size_t]
+    assert fn(C.byref(info), err, 256) == 1
+    assert info.name and info.architecture == b"sm_100"
+    assert info.recommended_working_set == info.max_buffer_length > (100 << 30)
+    assert info.physical_memory > (1 << 30)
+    assert (info.apple_gpu_family, info.metal4, info.unified_memory) == (0, 0, 0)
+    assert fn(None, err, 256) == 0
+
+
+def test_a_bounded_wait_that_runs_out_fails_the_submit_and_leaves_the_context_usable(gpu, pkg):
+    """The cross-rank barrier with a peer that never arrives: a two-rank table whose flag words
+    are both local buffers, nobody plays rank 1, and a budget of a few milliseconds. The kernel
+    returns by itself, h3_gpu_submit reports "peer barrier gave up", the status word is cleared
+    and the next command runs. Nothing faults, hangs or is killed."""
+    lib = gpu.lib
+    flags = [gpu.f32(np.zeros(16, np.float32)) for _ in range(2)]     # 16 zeroed 32-bit words each
+    peers = pkg.UlyssesPeers()
+    peers.world, peers.rank, peers.rows_local = 2, 0, 1
+    for r in range(2):
+        peers.flags[r] = flags[r].pointer
+    assert lib.h3x_set_wait_budget_cycles(gpu.handle, 0, 4_000_000) == 1      # ~2 ms of SM clock
+    gpu.begin()
+    assert lib.h3x_set_wait_budget_cycles(gpu.handle, 0, 1) == 0              # not inside a command
+    gpu.op("h3x_peer_barrier", peers)
+    assert lib.h3_gpu_submit(gpu.handle) == 0
+    assert "peer barrier gave up" in gpu.error()
+    assert lib.h3x_kernel_status(gpu.handle) == 0                             # cleared by the failed submit
+    a = gpu.bf16(o.normal_bf16(64, 1))
+    out = gpu.new(64, pkg.BF16)
+    gpu.begin()
+    gpu.op("add_bf16", out, a, a, 64)
+    gpu.submit()                                                              # the context still works
+    assert np.array_equal(out.read(), o.add_bf16(o.normal_bf16(64, 1), o.normal_bf16(64, 1)))
+    # the same barrier passes once the peer's word is there: rank 1 "arrives" by a host write of
+    # the next epoch (2) into this rank's slot for it
+    flags[0].write(np.array([2], np.uint32).view(np.float32), offset=1)
+    gpu.begin()
+    gpu.op("h3x_peer_barrier", peers)
+    gpu.submit()

@@ -197,6 +197,9 @@ def test_token_pool_and_expand(gpu, pkg):
     (257, 5376, 768, False),    # model K, three row tiles with a 1-row tail
     (128, 200, 264, False),     # K tail inside a 64-element slab
     (300, 7168, 5376, False),   # attention out-projection shape
+    (42, 2688, 96768, True),    # adaLN modulation projection at its largest row count
+                                # (h3_dit_schedule.c:264-301: rows = time rows <= 42)
+    (2, 2688, 96768, True),     # ... and at the two time rows of a single-step run
 ])
 def test_linear_bf16(gpu, pkg, rows, k, n, bias):
     x, w = bf(rows * k, 1), bf(n * k, 2, 0.05)

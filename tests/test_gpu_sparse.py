@@ -131,6 +131,30 @@ def test_masked_attention_matches_oracle(pkg, seq, kind):
     assert_aggregate_close(other, dense_small, "dense call while a mask for other rows is registered")
 
 
+def test_query_blocks_that_list_nothing_give_zero_rows(pkg):
+    """A 128-row query block with an empty list attends nothing: its rows are zeros, not NaN
+    (h3_cuda_attention.cu:1790,1800). Covered: an empty block beside a listed one in the same
+    CTA, a CTA whose two blocks are both empty, and blocks past the end of a short ptr array."""
+    seq, heads = 900, 2                      # 8 query blocks (the last ragged) = 4 CTAs
+    q, k, v = qkv(seq, heads, 9)
+    kt = (seq + 63) // 64
+    lists = [[0, 3], [], [], [], [1, kt - 1], [2]]       # blocks 6 and 7 are not listed at all
+    ptr, idx = csr(lists)
+    want = o.sdpa_bf16_sparse(q, k, v, seq, heads, 128, SCALE,
+                              *csr(lists + [[], []]), round_p=1)
+    gpu = pkg.Gpu(0)
+    try:
+        assert set_sparse(gpu, ptr, idx, seq) == 1
+        got = run_sdpa(pkg, gpu, q, k, v, seq, heads)
+    finally:
+        gpu.close()
+    rows = got.reshape(seq, heads * 128)
+    for block in (1, 2, 3, 6, 7):
+        assert not rows[block * 128:(block + 1) * 128].any(), f"query block {block} is not zero"
+    assert rows[:128].any() and rows[4 * 128:6 * 128].any()
+    assert_aggregate_close(got, want, "sparse mask with empty query blocks")
+
+
 @pytest.mark.skipif(not REF_CUDA.exists(), reason="reference CUDA backend was not built")
 def test_masked_attention_matches_reference_cuda_backend(pkg):
     seq, heads = 1664, 8

@@ -18,22 +18,43 @@ def gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("mode", ["nccl", "push"])
-@pytest.mark.parametrize("rows", [300, 301])      # 301: the last rank holds a padding row
-def test_sharded_block_matches_oracle(rows, mode):
-    n = gpu_count()
-    if n < 2:
-        pytest.skip("needs at least two GPUs")
-    world = 2
+def run_worker(world, *argv):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     port = 29600 + os.getpid() % 300
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                           f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                          "--master-port", str(port), str(ROOT / "tests" / "ulysses_worker.py"), str(rows), mode],
-                         capture_output=True, text=True, timeout=600, env=env)
+                          "--master-port", str(port), str(ROOT / "tests" / "ulysses_worker.py"),
+                          *map(str, argv)],
+                         capture_output=True, text=True, timeout=900, env=env)
     print(res.stdout[-2000:])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert "PASS" in res.stdout
+
+
+@pytest.mark.parametrize("mode", ["nccl", "push"])
+@pytest.mark.parametrize("rows", [300, 301])      # 301: the last rank holds a padding row
+def test_sharded_block_matches_oracle(rows, mode):
+    if gpu_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    run_worker(2, rows, mode, "small")
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_sharded_block_matches_oracle_on_more_ranks(world):
+    """2 heads / 1 head per rank, ragged last shard (301 rows over 4 or 8 ranks)."""
+    if gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_worker(world, 301, "push", "small")
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("mode", ["push", "nccl"])
+def test_full_width_sharded_block_matches_single_gpu(world, mode):
+    """The model's width (56 heads: 28 / 14 / 7 per rank; at 8 ranks the 21 q/k/v units of a
+    rank leave the last 256-column QKV tile half empty) at S = 1,664 (208 rows per rank at 8)."""
+    if gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_worker(world, 1664, mode, "full")
 
 
 @pytest.mark.parametrize("world", [2, 4])

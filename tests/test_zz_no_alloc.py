@@ -5,8 +5,11 @@ thread where a driver allocation is not allowed; for them the library offers a f
 entry point whose scratch is a fixed array inside the library image. This test calls it
 through the C ABI twice in a row (with different inputs, so anything left in the shared
 scratch by the first call would show) and requires the results to equal those of the
-ordinary entry point, h3_gpu_adaln_linear_bf16, bit for bit; it also checks that a call
-beyond the built-in limit is rejected with a message rather than run.
+ordinary entry point, h3_gpu_adaln_linear_bf16, bit for bit. The calls include one that fills
+the built-in scratch to its last element and one whose width is not a multiple of 8 (the
+projection then takes the scalar route). Around every call of the new entry point the free
+device memory and the context's allocation counters must not move, and a call beyond the
+built-in limit must be rejected with a message rather than run.
 
 Collected last on purpose (file name), so that a run stopping at the first failure has
 already run every other test. It creates its own context and passes on its own as well as
@@ -34,11 +37,15 @@ def final_head_inputs(seed, rows, width, out_dim, slots, offset):
 def test_no_alloc_final_head_matches_the_allocating_entry_point():
     import __graft_entry__ as entry
     pkg = entry.load_package()
+    import torch
+    torch.cuda.init()
     gpu = pkg.Gpu(0)
     try:
         slots = 2
-        # two calls in a row; the second is smaller and offset so stale scratch would matter
-        for seed, rows, width, out_dim, offset in ((11, 96, 5376, 96, 0), (23, 40, 2048, 32, 2048)):
+        # calls in a row; the second is smaller and offset so stale scratch would matter, the
+        # third uses every element of the 4 Mi scratch, the fourth has an odd width
+        for seed, rows, width, out_dim, offset in ((11, 96, 5376, 96, 0), (23, 40, 2048, 32, 2048),
+                                                   (31, 2048, 2048, 32, 0), (37, 10, 1001, 9, 3)):
             x, norm, mod, w, b, row_map = final_head_inputs(seed, rows, width, out_dim, slots, offset)
             tx, tn, tm, tw, tb = (gpu.bf16(a) for a in (x, norm, mod, w, b))
             tr = gpu.u32(row_map)
@@ -46,10 +53,19 @@ def test_no_alloc_final_head_matches_the_allocating_entry_point():
             for name in ("h3_gpu_adaln_linear_bf16", "h3x_adaln_linear_bf16_noalloc"):
                 out = gpu.bf16(np.zeros(rows * out_dim, np.uint16))
                 inv = gpu.f32(np.zeros(rows, np.float32))
+                torch.cuda.synchronize()
+                free_before, counters_before = torch.cuda.mem_get_info(0)[0], gpu.stats()
                 gpu.begin()
                 gpu.op(name, out, inv, tx, offset, tn, tm, tr, tw, tb, rows, width, out_dim, slots,
                        0, 1, 1e-5)
                 gpu.submit()
+                if name.endswith("noalloc"):
+                    # the allocating entry point ran the same kernels just before, so nothing is
+                    # loaded lazily here: any change would be an allocation
+                    counters = gpu.stats()
+                    assert torch.cuda.mem_get_info(0)[0] == free_before, "device memory was allocated"
+                    assert counters.tensor_allocations == counters_before.tensor_allocations
+                    assert counters.allocated_bytes == counters_before.allocated_bytes
                 results[name] = (out.read(), inv.read())
             want, got = results["h3_gpu_adaln_linear_bf16"], results["h3x_adaln_linear_bf16_noalloc"]
             assert np.array_equal(got[0], want[0]), f"output differs (rows={rows}, width={width})"

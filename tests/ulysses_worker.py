@@ -2,8 +2,11 @@
 
 Every rank holds a row slice of one DiT block's input, runs the block through the host
 driver with the exchange around attention (argv[2]: nccl = pack + all-to-all + unpack,
-push = peer stores from the kernels' epilogues), and rank 0 checks the gathered
-output against the CPU oracle's single-device block (per-block bar)."""
+push = peer stores from the kernels' epilogues), and rank 0 checks the gathered output
+(per-block bar). argv[3] picks the case: "small" (hidden 512, 8 heads) is checked against the
+CPU oracle's single-device block; "full" (the model's width: hidden 5376, 56 heads, FFN 14336,
+so 28 / 14 / 7 heads per rank at 2 / 4 / 8 ranks) against the same block run unsharded on
+rank 0, which the single-GPU tests pin to the oracle and to the reference's CUDA backend."""
 import os
 import sys
 from pathlib import Path
@@ -17,15 +20,18 @@ for p in (ROOT, ROOT / "oracle", ROOT / "tests"):
     sys.path.insert(0, str(p))
 
 import h3_oracle as o  # noqa: E402
-from bench import NcclExchange, TorchMemory  # noqa: E402
-from block_case import make_block_case, upload_block  # noqa: E402
+from block_case import make_block_case, run_block_on_gpu, upload_block  # noqa: E402
 from parity import block_metrics  # noqa: E402
 import __graft_entry__ as entry  # noqa: E402
+
+entry.load_package()
+from h3c_b200.plumbing import NcclExchange, TorchMemory  # noqa: E402
 
 
 def main():
     rows = int(sys.argv[1]) if len(sys.argv) > 1 else 301
     mode = sys.argv[2] if len(sys.argv) > 2 else "nccl"
+    full = len(sys.argv) > 3 and sys.argv[3] == "full"
     pkg = entry.load_package()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -33,9 +39,11 @@ def main():
     device = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=device)
     gpu = pkg.Gpu(local)
-    mem = TorchMemory(torch, pkg, gpu, device)
-    case = make_block_case(rows=rows, text_rows=37, heads=8, hidden=512, ffn=1024, seed=5)
-    shape = pkg.DitShape(hidden=512, heads=8, ffn=1024, blocks=1)
+    mem = TorchMemory(torch, gpu, device)
+    heads, hidden, ffn = (56, 5376, 14336) if full else (8, 512, 1024)
+    case = make_block_case(rows=rows, text_rows=37, heads=heads, hidden=hidden, ffn=ffn, seed=5,
+                           fast=full)
+    shape = pkg.DitShape(hidden=hidden, heads=heads, ffn=ffn, blocks=1)
     if mode == "push":
         def gather(obj):
             out = [None] * world
@@ -56,7 +64,7 @@ def main():
     row_map = gpu.u32(local_slice(case.row_map, 1, np.uint32))
     cos = gpu.bf16(local_slice(case.rope_cos, 48, np.uint16))
     sin = gpu.bf16(local_slice(case.rope_sin, 48, np.uint16))
-    dit.hidden.write(local_slice(case.hidden, 512, np.uint16))
+    dit.hidden.write(local_slice(case.hidden, hidden, np.uint16))
     dist.barrier()
     gpu.begin()
     dit.run_block(w, row_map, cos, sin, False, None)
@@ -66,13 +74,17 @@ def main():
     dist.all_gather(gathered, mine)
     ok = True
     if rank == 0:
-        full = np.concatenate([g.cpu().numpy().astype(np.uint16) for g in gathered])[:rows * 512]
-        want = o.dit_block(case.hidden, case.weights, case.row_map, case.rope_cos, case.rope_sin,
-                           rows=rows, width=512, heads=8, head_dim=128, ffn=1024, rope_half=48, round_p=1)
-        r, m = block_metrics(full, want)
+        got = np.concatenate([g.cpu().numpy().astype(np.uint16) for g in gathered])[:rows * hidden]
+        if full:
+            want = run_block_on_gpu(pkg, gpu, case)
+        else:
+            want = o.dit_block(case.hidden, case.weights, case.row_map, case.rope_cos, case.rope_sin,
+                               rows=rows, width=hidden, heads=heads, head_dim=128, ffn=ffn,
+                               rope_half=48, round_p=1)
+        r, m = block_metrics(got, want)
         ok = r <= 1e-2 and m <= 5e-2
-        print(f"ulysses {mode} world={world} rows={rows}: rel_l2={r:.3e} max_abs={m:.3e} {'PASS' if ok else 'FAIL'}",
-              flush=True)
+        print(f"ulysses {mode} world={world} rows={rows} heads={heads}: rel_l2={r:.3e} max_abs={m:.3e} "
+              f"{'PASS' if ok else 'FAIL'}", flush=True)
     dist.barrier()
     if mode == "push":
         exchange.close()
