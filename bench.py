@@ -421,12 +421,14 @@ def kernel_timings(torch, pkg, gpu, shape, dit, step, exchange, sequence, world,
     return out
 
 
-def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, repeats=10):
+def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, rounds=3, repeats=8):
     """The same projections and attention through the reference's CUDA backend (cuBLASLt GEMMs,
-    mma.sync attention; oracle/_ref/libh3ref.so) on the same GPU with the same tensors' contents:
-    name -> ms per launch, CUDA events. Its linears carry no fused epilogue (the norm + RoPE and
-    the SwiGLU are separate kernels there, not timed here), so each figure is a lower bound of
-    what the reference spends on the op this library does in one launch."""
+    mma.sync attention; oracle/_ref/libh3ref.so) on the same GPU, timed back to back with this
+    library's launch of the same op: per op `rounds` alternations of (ours x repeats, theirs x
+    repeats), CUDA events, so both see the same clocks and temperature. Returns
+    name -> {"ms": ours, "reference_cuda_ms": theirs}. The reference's linears carry no fused
+    epilogue (its norm + RoPE and its SwiGLU are separate kernels, not timed here), so its
+    figure is a lower bound of what it spends on the op this library does in one launch."""
     if not REF_CUDA.exists():
         return None
     s, rows, w = shape, dit.rows_local, step.blocks[0]
@@ -443,7 +445,7 @@ def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, repeats=10):
                    (("qkv", 3 * s.inner * s.hidden), ("out", s.hidden * s.inner),
                     ("fc1", 2 * s.ffn * s.hidden), ("fc2", s.hidden * s.ffn))}
         q, k, v = (copy(t, rows * s.inner) for t in (dit.query, dit.key, dit.value))
-        ops = {
+        theirs = {
             "qkv_proj_norm_rope": lambda: ref.op("linear_bf16", wide, x, weights["qkv"], None, rows,
                                                  s.hidden, 3 * s.inner),
             "mlp_fc1_swiglu": lambda: ref.op("linear_bf16", wide, x, weights["fc1"], None, rows,
@@ -455,7 +457,28 @@ def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, repeats=10):
             "attention": lambda: ref.op("sdpa_bf16", heads_in, q, k, v, sequence, s.heads,
                                         s.head_dim, s.scale),
         }
-        return {name: time_kernel(torch, ref, fn, 0.0, repeats)[0] for name, fn in ops.items()}
+        ours = {
+            "qkv_proj_norm_rope": lambda: gpu.op(
+                "grouped_qkv_linear_rope_bf16", dit.query, dit.key, dit.value, dit.qkv, dit.mod_attention,
+                w.qkv, w.q_norm, w.k_norm, step.rope_cos, step.rope_sin, rows, s.hidden, s.heads,
+                s.head_dim, s.rope_half, s.eps),
+            "mlp_fc1_swiglu": lambda: gpu.op("h3x_linear_swiglu_bf16", dit.qkv, dit.mod_attention, w.fc1,
+                                             rows, s.hidden, s.ffn),
+            "mlp_fc2": lambda: gpu.op("linear_bf16", dit.attention_output, dit.qkv, w.fc2, None, rows,
+                                      s.ffn, s.hidden),
+            "gemm_out_proj": lambda: gpu.op("linear_bf16", dit.attention_output, dit.attention_heads,
+                                            w.out, None, rows, s.inner, s.hidden),
+            "attention": lambda: gpu.op("sdpa_bf16", dit.attention_heads, dit.query, dit.key, dit.value,
+                                        sequence, s.heads, s.head_dim, s.scale),
+        }
+        out = {}
+        for name in theirs:
+            a, b = [], []
+            for _ in range(rounds):
+                a.append(time_kernel(torch, gpu, ours[name], 0.0, repeats)[0])
+                b.append(time_kernel(torch, ref, theirs[name], 0.0, repeats)[0])
+            out[name] = {"ms": statistics.mean(a), "reference_cuda_ms": statistics.mean(b)}
+        return out
     except Exception as err:                      # a supplementary figure must not sink the run
         return {"unavailable": str(err)[:200]}
     finally:
@@ -698,7 +721,8 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         def kernel_entry(name, v):
             e = {"ms": v[0], "tflops": v[1], "frac_of_burst_peak": v[1] / peaks["bf16_tflops"]}
             if ref_ops and name in ref_ops:
-                e["reference_cuda_ms"] = ref_ops[name]
+                # this library and the reference's CUDA backend timed alternately, same GPU state
+                e["paired_with_reference_cuda"] = ref_ops[name]
             return e
         kernel_lines = {k: kernel_entry(k, v) for k, v in kernels.items()}
         if ref_ops and "unavailable" in ref_ops:

@@ -40,6 +40,11 @@ struct h3b_pinned_slot {
     bool pending = false;
 };
 
+struct h3b_loader;                  /* pinned ring + copy stream of the file loads */
+void h3b_loader_free(h3b_loader *loader);
+struct h3b_op_profile;              /* per-op device timing, on when H3_PROFILE=2 */
+void h3b_profile_record(struct h3_gpu *gpu, const char *what);
+
 struct h3_gpu {
     int device = 0;
     int sm_count = 0;
@@ -52,6 +57,12 @@ struct h3_gpu {
     /* grow-only scratch for intermediates of composite ops (MLP, final head) */
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
+    /* F32 partial tiles + counters of the GEMMs' split tail round (allocated by the first
+     * launch that splits; at most `workers` partial tiles of 128 KiB per 128 rows) */
+    static constexpr size_t kSplitScratchBytes = size_t(40) << 20;
+    static constexpr size_t kSplitCounterBytes = 4096;
+    void *split_scratch = nullptr;
+    int allocation_barred = 0;      /* set while an entry point that must not allocate runs */
 
     /* exact-size cache of freed device blocks; reuse is ordered by the stream */
     std::unordered_multimap<size_t, void *> cache;
@@ -82,6 +93,8 @@ struct h3_gpu {
 
     char profile_label[128] = {0};
     double profile_mark = 0.0;
+    h3b_loader *loader = nullptr;   /* created by the first file load */
+    h3b_op_profile *op_profile = nullptr;
 };
 
 double h3b_now();
@@ -110,6 +123,7 @@ enum h3b_kind { H3B_DIRECT = 0, H3B_LINEAR = 1, H3B_CONV = 2, H3B_SDPA = 3 };
 inline int h3b_launched(h3_gpu *gpu, const char *what, h3b_kind kind = H3B_DIRECT) {
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return h3b_fail_cuda(gpu, what, status);
+    if (gpu->op_profile) h3b_profile_record(gpu, what);
     switch (kind) {
         case H3B_LINEAR: gpu->stats.mps_linear_dispatches++; break;
         case H3B_CONV: gpu->stats.mps_conv_dispatches++; break;

@@ -14,6 +14,11 @@
 #include "h3b_common.cuh"
 
 #include <algorithm>
+#include <atomic>
+#include <map>
+#include <string>
+#include <condition_variable>
+#include <thread>
 
 #include <cerrno>
 #include <cstdlib>
@@ -27,6 +32,74 @@ double h3b_now() {
     timespec t;
     clock_gettime(CLOCK_MONOTONIC, &t);
     return double(t.tv_sec) + double(t.tv_nsec) * 1e-9;
+}
+
+/* ------------------------------------------------------------ op profile */
+/* H3_PROFILE=2: device time per op name. Every launch is followed by an event on the
+ * context's stream; at submit the gaps between consecutive events (the stream is in order, so
+ * a gap is the op's duration plus any launch bubble before it) are added up per name, and
+ * h3_gpu_profile_mark / h3_gpu_free print the table. The reference prints wall and wait time
+ * per phase (h3_gpu_cuda.cu:21-45,919-933); this adds where inside a phase the device time
+ * goes. Off by default: one event record per launch otherwise. */
+struct h3b_op_profile {
+    struct Total { double ms = 0.0; uint64_t count = 0; };
+    std::vector<cudaEvent_t> pool;
+    std::vector<std::pair<const char *, cudaEvent_t>> marks;   /* first = nullptr: command begin */
+    std::map<std::string, Total> totals;
+
+    cudaEvent_t take() {
+        cudaEvent_t e = nullptr;
+        if (!pool.empty()) { e = pool.back(); pool.pop_back(); return e; }
+        if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        return e;
+    }
+    void collect() {       /* the stream has been synchronised */
+        cudaEvent_t previous = nullptr;
+        for (auto &mark : marks) {
+            if (mark.first && previous) {
+                float ms = 0.0f;
+                if (cudaEventElapsedTime(&ms, previous, mark.second) == cudaSuccess) {
+                    Total &t = totals[mark.first];
+                    t.ms += ms;
+                    t.count++;
+                } else {
+                    cudaGetLastError();
+                }
+            }
+            previous = mark.second;
+        }
+        for (auto &mark : marks) pool.push_back(mark.second);
+        marks.clear();
+    }
+    void print(const char *label, const char *phase) {
+        if (totals.empty()) return;
+        std::vector<std::pair<std::string, Total>> rows(totals.begin(), totals.end());
+        std::sort(rows.begin(), rows.end(), [](const auto &a, const auto &b) { return a.second.ms > b.second.ms; });
+        double sum = 0.0;
+        for (auto &r : rows) sum += r.second.ms;
+        fprintf(stderr, "h3b200: [%s] %s: %.3f ms of device time in %zu op names\n", label, phase, sum, rows.size());
+        for (auto &r : rows)
+            fprintf(stderr, "h3b200:   %-40s %10.3f ms %5.1f %% %8llu launches %9.4f ms each\n", r.first.c_str(),
+                    r.second.ms, 100.0 * r.second.ms / (sum > 0 ? sum : 1), (unsigned long long)r.second.count,
+                    r.second.ms / double(r.second.count ? r.second.count : 1));
+        totals.clear();
+    }
+    ~h3b_op_profile() {
+        for (auto &mark : marks) cudaEventDestroy(mark.second);
+        for (cudaEvent_t e : pool) cudaEventDestroy(e);
+    }
+};
+
+void h3b_profile_record(h3_gpu *gpu, const char *what) {
+    h3b_op_profile *p = gpu->op_profile;
+    cudaEvent_t e = p->take();
+    if (!e) return;
+    if (cudaEventRecord(e, gpu->stream) != cudaSuccess) {
+        cudaGetLastError();
+        p->pool.push_back(e);
+        return;
+    }
+    p->marks.emplace_back(what, e);
 }
 
 /* ------------------------------------------------------------ allocator */
@@ -186,6 +259,8 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
         return fail("cannot allocate the kernel status word", status);
     }
     gpu->profile_mark = h3b_now();
+    const char *profile = getenv("H3_PROFILE");
+    if (profile && atoi(profile) >= 2) gpu->op_profile = new (std::nothrow) h3b_op_profile();
     return gpu;
 }
 
@@ -194,10 +269,16 @@ extern "C" void h3_gpu_free(h3_gpu *gpu) {
     cudaSetDevice(gpu->device);
     cudaStreamSynchronize(gpu->stream);
     if (gpu->workspace) cudaFree(gpu->workspace);
+    if (gpu->split_scratch) cudaFree(gpu->split_scratch);
     cache_evict_all(gpu);
     for (h3b_pinned_slot &slot : gpu->slots) {
         if (slot.host) cudaFreeHost(slot.host);
         if (slot.done) cudaEventDestroy(slot.done);
+    }
+    h3b_loader_free(gpu->loader);
+    if (gpu->op_profile) {
+        gpu->op_profile->print(gpu->profile_label[0] ? gpu->profile_label : "gpu", "since the last mark");
+        delete gpu->op_profile;
     }
     if (gpu->status_device) cudaFree(gpu->status_device);
     if (gpu->sparse_cta_ptr) cudaFree(gpu->sparse_cta_ptr);
@@ -239,6 +320,7 @@ extern "C" int h3_gpu_begin(h3_gpu *gpu) {
     gpu->error[0] = '\0';
     gpu->active = 1;
     gpu->command_start = h3b_now();
+    if (gpu->op_profile) h3b_profile_record(gpu, nullptr);
     return 1;
 }
 
@@ -266,6 +348,7 @@ extern "C" int h3_gpu_submit(h3_gpu *gpu) {
     gpu->stats.command_wait_seconds += completed - committed;
     gpu->stats.gpu_seconds += completed - committed;
     if (status != cudaSuccess) return h3b_fail_cuda(gpu, "command execution", status);
+    if (gpu->op_profile) gpu->op_profile->collect();
     if (kernel_status != H3B_STATUS_OK) {
         cudaMemsetAsync(gpu->status_device, 0, sizeof(int), gpu->stream);
         gpu->status_seen = kernel_status;
@@ -306,6 +389,7 @@ extern "C" void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase) {
             (unsigned long long)gpu->stats.direct_dispatches,
             (unsigned long long)gpu->stats.mps_linear_dispatches,
             (unsigned long long)gpu->stats.mps_sdpa_dispatches);
+    if (gpu->op_profile) gpu->op_profile->print(gpu->profile_label[0] ? gpu->profile_label : "gpu", phase);
     gpu->profile_mark = now;
 }
 
@@ -507,14 +591,79 @@ extern "C" int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *t, size_t o, const 
 }
 
 /* ------------------------------------------------------------ file loads */
-/* Payload bytes are read with pread() into a pinned bounce buffer, 16 MiB at a
- * time on two alternating buffers, and copied to the device on a private
- * stream, so a load may run on an I/O thread while the main thread keeps
- * issuing kernels on tensors that are not being filled.
+/* A payload is cut into 16 MiB chunks on a 4 KiB-aligned grid of the file. Up to four reader
+ * threads pread() chunks into a ring of pinned buffers that belongs to the context (allocated
+ * on first use, kept), while the calling thread uploads finished chunks in order with
+ * cudaMemcpyAsync on a private copy stream: the disk, the page-cache copy and the host->device
+ * DMA overlap, and nothing is allocated per call. Reads go through O_DIRECT where the file
+ * system takes it (the raw device rate instead of the page cache's; every chunk is an aligned
+ * superset of its payload bytes), else through the page cache; H3B_DIRECT_IO=0 forces the
+ * latter. Replaces the reference's loader (h3_gpu_cuda.cu:455-689: whole tensor into one pinned
+ * staging buffer with up to 16 threads, then one synchronous copy).
+ * A load may run on an I/O thread while the context's thread keeps issuing kernels on tensors
+ * that are not being filled; loads of one context are serialised among themselves.
  * after_context: the first copy waits (on the device, through an event) for the work queued
  * on the context's stream at the time of the call, so kernels that still read the tensor's
  * previous contents finish first. The streaming entry point does not wait: its contract is a
  * target that is idle on the context's stream, so that the upload overlaps the running block. */
+
+struct h3b_loader {
+    static constexpr int kBuffers = 6;
+    static constexpr size_t kChunk = size_t(16) << 20;
+    static constexpr size_t kAlign = 4096;
+    void *pinned[kBuffers] = {};
+    cudaEvent_t uploaded[kBuffers] = {};
+    cudaStream_t stream = nullptr;
+    bool ready = false;
+    std::mutex mutex;                       /* one load at a time per context */
+
+    bool prepare() {
+        if (ready) return true;
+        if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) return false;
+        for (int i = 0; i < kBuffers; i++)
+            if (cudaMallocHost(&pinned[i], kChunk + 2 * kAlign) != cudaSuccess ||
+                cudaEventCreateWithFlags(&uploaded[i], cudaEventDisableTiming) != cudaSuccess)
+                return false;
+        ready = true;
+        return true;
+    }
+    void release() {
+        for (int i = 0; i < kBuffers; i++) {
+            if (pinned[i]) cudaFreeHost(pinned[i]);
+            if (uploaded[i]) cudaEventDestroy(uploaded[i]);
+            pinned[i] = nullptr;
+            uploaded[i] = nullptr;
+        }
+        if (stream) cudaStreamDestroy(stream);
+        stream = nullptr;
+        ready = false;
+    }
+};
+
+void h3b_loader_free(h3b_loader *loader) {
+    if (!loader) return;
+    loader->release();
+    delete loader;
+}
+
+/* pread of [offset, offset + bytes): 0 on success, errno on error, -1 when the file ended
+ * before `need` bytes (an O_DIRECT span is rounded up past the payload, so it may be cut). */
+static int read_span(int fd, unsigned char *dst, uint64_t offset, size_t bytes, size_t need) {
+    size_t got = 0;
+    while (got < bytes) {
+        ssize_t n = pread(fd, dst + got, bytes - got, off_t(offset + got));
+        if (n < 0 && errno == EINTR) continue;
+        if (n < 0) return errno;
+        if (n == 0) return got >= need ? 0 : -1;
+        got += size_t(n);
+    }
+    return 0;
+}
+
+static bool direct_io_wanted() {
+    const char *v = getenv("H3B_DIRECT_IO");
+    return !(v && *v && strcmp(v, "0") == 0);
+}
 
 static int fill_from_file(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
                           size_t elements, h3_gpu_dtype dtype, char *error, size_t error_size,
@@ -523,59 +672,118 @@ static int fill_from_file(h3_gpu_tensor *tensor, const char *path, uint64_t file
         if (error && error_size) snprintf(error, error_size, "%s: %s", what, path ? path : "(null)");
         return 0;
     };
-    if (!tensor || !path || tensor->dtype != dtype || elements > tensor->elements)
+    if (!tensor || !path || tensor->dtype != dtype || elements > tensor->elements || !tensor->owner)
         return fail("invalid tensor file read");
-    size_t bytes = elements * h3b_item_size(dtype);
-    int fd = open(path, O_RDONLY);
-    if (fd < 0) return fail("cannot open tensor file");
+    const size_t bytes = elements * h3b_item_size(dtype);
+    if (!bytes) return 1;
     h3_gpu *gpu = tensor->owner;
-    if (gpu) cudaSetDevice(gpu->device);
-    const size_t chunk = size_t(16) << 20;
-    void *bounce[2] = {nullptr, nullptr};
-    cudaEvent_t done[2] = {nullptr, nullptr};
-    cudaStream_t stream = nullptr;
+    if (!gpu->loader) gpu->loader = new (std::nothrow) h3b_loader();
+    h3b_loader *ld = gpu->loader;
+    if (!ld) return fail("out of memory for the file loader of");
+    std::lock_guard<std::mutex> serial(ld->mutex);
+    cudaSetDevice(gpu->device);
+    if (!ld->prepare()) {
+        cudaGetLastError();
+        return fail("cannot allocate staging memory for");
+    }
+    const int fd = open(path, O_RDONLY | O_CLOEXEC);
+    if (fd < 0) return fail("cannot open tensor file");
+    int fd_direct = direct_io_wanted() ? open(path, O_RDONLY | O_CLOEXEC | O_DIRECT) : -1;
+
     int ok = 1;
-    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) ok = 0;
-    for (int i = 0; ok && i < 2; i++)
-        if (cudaMallocHost(&bounce[i], chunk) != cudaSuccess ||
-            cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) != cudaSuccess)
-            ok = 0;
-    if (!ok) fail("cannot allocate staging memory for");
-    if (ok && gpu && after_context) {
+    if (after_context) {
         cudaEvent_t queued = nullptr;
         if (cudaEventCreateWithFlags(&queued, cudaEventDisableTiming) != cudaSuccess ||
             cudaEventRecord(queued, gpu->stream) != cudaSuccess ||
-            cudaStreamWaitEvent(stream, queued, 0) != cudaSuccess)
+            cudaStreamWaitEvent(ld->stream, queued, 0) != cudaSuccess)
             ok = fail("cannot order the upload after the context's stream for");
         if (queued) cudaEventDestroy(queued);
     }
-    size_t moved = 0;
-    for (int turn = 0; ok && moved < bytes; turn ^= 1) {
-        size_t want = bytes - moved < chunk ? bytes - moved : chunk;
-        if (cudaEventSynchronize(done[turn]) != cudaSuccess) { ok = fail("staging wait failed for"); break; }
-        size_t got = 0;
-        while (got < want) {
-            ssize_t n = pread(fd, static_cast<char *>(bounce[turn]) + got, want - got,
-                              off_t(file_offset + moved + got));
-            if (n < 0 && errno == EINTR) continue;
-            if (n <= 0) break;
-            got += size_t(n);
+
+    /* chunk c = file bytes [grid0 + c * kChunk, grid0 + (c + 1) * kChunk) cut to the payload */
+    constexpr size_t kChunk = h3b_loader::kChunk, kAlign = h3b_loader::kAlign;
+    constexpr int kBuffers = h3b_loader::kBuffers;
+    const uint64_t grid0 = file_offset & ~uint64_t(kAlign - 1);
+    const uint64_t payload_end = file_offset + bytes;
+    const size_t chunks = size_t((payload_end - grid0 + kChunk - 1) / kChunk);
+    std::vector<int> state(chunks, 0);          /* 0 pending, 1 read, <0 failed */
+    std::vector<size_t> skip(chunks, 0);        /* payload offset inside the chunk's buffer */
+    std::mutex m;
+    std::condition_variable cv;
+    size_t uploads_issued = 0;                  /* chunks whose copy has been enqueued */
+    bool abort_all = !ok;
+    std::atomic<bool> direct_refused(false);
+
+    auto reader = [&](size_t first, size_t stride) {
+        for (size_t c = first; c < chunks; c += stride) {
+            const int slot = int(c % kBuffers);
+            {   /* the slot is free once the copy of chunk c - kBuffers has finished */
+                std::unique_lock<std::mutex> lock(m);
+                cv.wait(lock, [&] { return abort_all || c < size_t(kBuffers) || uploads_issued + kBuffers > c; });
+                if (abort_all) return;
+            }
+            if (c >= size_t(kBuffers) && cudaEventSynchronize(ld->uploaded[slot]) != cudaSuccess) {
+                std::lock_guard<std::mutex> lock(m);
+                state[c] = -1; abort_all = true; cv.notify_all();
+                return;
+            }
+            const uint64_t begin = grid0 + uint64_t(c) * kChunk;
+            const uint64_t first_byte = begin > file_offset ? begin : file_offset;
+            const uint64_t last_byte = begin + kChunk < payload_end ? begin + kChunk : payload_end;
+            unsigned char *dst = static_cast<unsigned char *>(ld->pinned[slot]);
+            int rc = EINVAL;
+            if (fd_direct >= 0 && !direct_refused.load()) {
+                const uint64_t span_end = (last_byte + kAlign - 1) & ~uint64_t(kAlign - 1);
+                rc = read_span(fd_direct, dst, begin, size_t(span_end - begin), size_t(last_byte - begin));
+                if (rc == EINVAL) direct_refused.store(true);     /* the file system refuses O_DIRECT */
+                else skip[c] = size_t(first_byte - begin);
+            }
+            if (rc == EINVAL) {
+                rc = read_span(fd, dst, first_byte, size_t(last_byte - first_byte), size_t(last_byte - first_byte));
+                skip[c] = 0;
+            }
+            std::lock_guard<std::mutex> lock(m);
+            state[c] = rc == 0 ? 1 : -1;
+            if (rc != 0) abort_all = true;
+            cv.notify_all();
+            if (rc != 0) return;
         }
-        if (got != want) { ok = fail("short read from"); break; }
-        if (cudaMemcpyAsync(static_cast<char *>(tensor->data) + moved, bounce[turn], want,
-                            cudaMemcpyHostToDevice, stream) != cudaSuccess ||
-            cudaEventRecord(done[turn], stream) != cudaSuccess) {
+    };
+
+    const size_t reader_count = chunks < 4 ? chunks : 4;
+    std::vector<std::thread> readers;
+    if (ok && chunks > 1)
+        for (size_t t = 0; t < reader_count; t++) readers.emplace_back(reader, t, reader_count);
+    for (size_t c = 0; ok && c < chunks; c++) {
+        if (chunks == 1) reader(0, 1);          /* small payloads are read inline */
+        {
+            std::unique_lock<std::mutex> lock(m);
+            cv.wait(lock, [&] { return state[c] != 0 || abort_all; });
+            if (state[c] != 1) { ok = fail("short or failed read from"); break; }
+        }
+        const int slot = int(c % kBuffers);
+        const uint64_t begin = grid0 + uint64_t(c) * kChunk;
+        const uint64_t first_byte = begin > file_offset ? begin : file_offset;
+        const uint64_t last_byte = begin + kChunk < payload_end ? begin + kChunk : payload_end;
+        if (cudaMemcpyAsync(static_cast<char *>(tensor->data) + (first_byte - file_offset),
+                            static_cast<unsigned char *>(ld->pinned[slot]) + skip[c],
+                            size_t(last_byte - first_byte), cudaMemcpyHostToDevice, ld->stream) != cudaSuccess ||
+            cudaEventRecord(ld->uploaded[slot], ld->stream) != cudaSuccess) {
             ok = fail("device upload failed for");
             break;
         }
-        moved += want;
+        std::lock_guard<std::mutex> lock(m);
+        uploads_issued = c + 1;
+        cv.notify_all();
     }
-    if (stream) cudaStreamSynchronize(stream);
-    for (int i = 0; i < 2; i++) {
-        if (bounce[i]) cudaFreeHost(bounce[i]);
-        if (done[i]) cudaEventDestroy(done[i]);
+    {
+        std::lock_guard<std::mutex> lock(m);
+        if (!ok) abort_all = true;
+        cv.notify_all();
     }
-    if (stream) cudaStreamDestroy(stream);
+    for (std::thread &t : readers) t.join();
+    if (cudaStreamSynchronize(ld->stream) != cudaSuccess && ok) ok = fail("device upload failed for");
+    if (fd_direct >= 0) close(fd_direct);
     close(fd);
     cudaGetLastError();
     return ok;
@@ -683,6 +891,7 @@ static int device_copy(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offset,
             static_cast<const unsigned char *>(src->data) + src_offset * item, elements * item,
             cudaMemcpyDeviceToDevice, gpu->stream);
         if (status != cudaSuccess) return h3b_fail_cuda(gpu, "device copy", status);
+        if (gpu->op_profile) h3b_profile_record(gpu, "copy");
     }
     gpu->stats.blit_copies++;
     return 1;

@@ -68,6 +68,14 @@ struct TcArgs {
     uint32_t k_blocks;
     uint32_t tiles_m, tiles_n;
     uint32_t group_m;     /* row-blocks walked together so their X slabs stay in L2 */
+    /* Tail round split along K: the last split_tiles tiles (what is left after the rounds in
+     * which every worker has a whole tile) are each computed by `split` workers, every one over
+     * 1/split of the K blocks. Workers 1..split-1 of a tile write their F32 partial tile to
+     * split_scratch and raise the tile's counter; worker 0 waits for them, adds the partials to
+     * its accumulator in a fixed order and runs the epilogue. split_tiles == 0: off. */
+    uint32_t split_tiles, split;
+    float *split_scratch;         /* [split_tiles][split - 1][tile rows][256] */
+    uint32_t *split_counters;     /* [split_tiles], zeroed before the launch */
     uint32_t up_offset;   /* SwiGLU: weight row of the first up column (= hidden) */
     /* QKV + norm + RoPE epilogue */
     uint16_t *q_out, *k_out, *v_out;
@@ -170,6 +178,99 @@ __device__ __forceinline__ void qkv_unit_epilogue(const TcArgs &args, uint32_t l
             *reinterpret_cast<uint4 *>(dst0 + size_t(row0 + r) * row_stride + chunk * 8) = val;
     }
     __syncwarp();
+}
+
+/* What a worker does in a given pass over its work: whole tiles first, then (at most) one
+ * K slice of a split tile. */
+struct WorkItem {
+    uint32_t tile, kb0, kb1, slot, part;    /* part: 0 = whole tile or the finishing slice */
+    bool split;
+};
+
+__device__ __forceinline__ bool next_item(const TcArgs &args, uint32_t worker, uint32_t workers,
+                                          uint32_t pass, WorkItem &item) {
+    const uint32_t whole = args.tiles_m * args.tiles_n - args.split_tiles;
+    const uint32_t tile = worker + pass * workers;
+    if (tile < whole) {
+        item = {tile, 0u, args.k_blocks, 0u, 0u, false};
+        return true;
+    }
+    /* whole is a multiple of workers whenever split_tiles != 0, so the split slice comes right
+     * after the last whole tile of every worker */
+    if (!args.split_tiles || tile - worker != whole || worker >= args.split_tiles * args.split) return false;
+    const uint32_t slot = worker / args.split, part = worker % args.split;
+    item = {whole + slot, part * args.k_blocks / args.split, (part + 1) * args.k_blocks / args.split,
+            slot, part, true};
+    return true;
+}
+
+/* Epilogue side of a split tile for one thread (= one accumulator row). row_in_tile: the row's
+ * index inside the tile; tile_rows: 128 (lone CTA) or 256 (CTA pair); arrivals: epilogue warps
+ * per worker (4 or 8). Returns true when this thread goes on to the normal epilogue (its
+ * accumulator now holds the whole sum), false when it only delivered a partial or gave up. */
+__device__ __forceinline__ bool split_tile_merge(const TcArgs &args, const WorkItem &item,
+                                                 uint32_t lane_addr, uint32_t row_in_tile,
+                                                 uint32_t tile_rows, uint32_t arrivals, uint32_t lane,
+                                                 volatile int *stop) {
+    const size_t tile_floats = size_t(tile_rows) * BN;
+    float *slot_base = args.split_scratch + size_t(item.slot) * (args.split - 1) * tile_floats;
+    uint32_t *counter = args.split_counters + item.slot;
+    if (item.part != 0) {
+        float *dst = slot_base + size_t(item.part - 1) * tile_floats + size_t(row_in_tile) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 8; v++)
+                __stcg(reinterpret_cast<uint4 *>(dst + c * 32) + v,
+                       make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(counter, 1u);
+        return false;
+    }
+    /* the finishing slice: wait for the other slices' partial tiles (bounded) */
+    uint32_t ok = 1;
+    if (lane == 0) {
+        const uint32_t want = (args.split - 1) * arrivals;
+        const long long start = clock64();
+        for (;;) {
+            uint32_t seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            if (seen >= want) break;
+            if (*stop || clock64() - start > args.wait_cycles) {
+                *stop = 1;
+                ok = 0;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + c * 32, r);
+        tmem_ld_wait();
+        for (uint32_t part = 1; part < args.split; part++) {
+            const float *src = slot_base + size_t(part - 1) * tile_floats + size_t(row_in_tile) * BN + c * 32;
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+                const uint4 p = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
+                r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + __uint_as_float(p.x));
+                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + __uint_as_float(p.y));
+                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + __uint_as_float(p.z));
+                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + __uint_as_float(p.w));
+            }
+        }
+        tmem_st32(lane_addr + c * 32, r);
+    }
+    tmem_st_wait_all();
+    return true;
 }
 
 /* One thread's share of a finished 128 x 256 accumulator tile: its row (TMEM lane) through the
@@ -295,7 +396,6 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
 
-    const uint32_t total_tiles = args.tiles_m * args.tiles_n;
     const uint32_t group_tiles = args.group_m * args.tiles_n;
 
     auto tile_coords = [&](uint32_t tile, uint32_t &m_blk, uint32_t &n_blk) {
@@ -311,10 +411,11 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool alive = true;
-            for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+            WorkItem item;
+            for (uint32_t pass = 0; alive && next_item(args, blockIdx.x, gridDim.x, pass, item); pass++) {
                 uint32_t m_blk, n_blk;
-                tile_coords(tile, m_blk, n_blk);
-                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                tile_coords(item.tile, m_blk, n_blk);
+                for (uint32_t kb = item.kb0; kb < item.kb1; kb++) {
                     if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop, args.wait_cycles)) { alive = false; break; }
                     uint32_t bar = full_bar + 8 * stage;
                     mbar_expect_tx(bar, A_BYTES + B_BYTES);
@@ -343,11 +444,12 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
-            for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+            WorkItem item;
+            for (uint32_t pass = 0; alive && next_item(args, blockIdx.x, gridDim.x, pass, item); pass++) {
                 if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop, args.wait_cycles))) break;
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                for (uint32_t kb = item.kb0; kb < item.kb1; kb++) {
                     if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop, args.wait_cycles))) {
                         alive = false;
                         break;
@@ -356,7 +458,7 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint32_t a_lo = a_lo0 + stage * (A_BYTES >> 4);
                     const uint32_t b_lo = b_lo0 + stage * (B_BYTES >> 4);
                     /* 16 BF16 along K = 32 bytes = 2 descriptor address units */
-                    if (kb == 0) umma_ss<false>(d_tmem, a_lo, b_lo, idesc, leader);
+                    if (kb == item.kb0) umma_ss<false>(d_tmem, a_lo, b_lo, idesc, leader);
                     else umma_ss<true>(d_tmem, a_lo, b_lo, idesc, leader);
 #pragma unroll
                     for (int k = 1; k < BK / 16; k++)
@@ -373,16 +475,18 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         /* ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ---- */
         const uint32_t quarter = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        WorkItem item;
+        for (uint32_t pass = 0; next_item(args, blockIdx.x, gridDim.x, pass, item); pass++) {
             uint32_t m_blk, n_blk;
-            tile_coords(tile, m_blk, n_blk);
+            tile_coords(item.tile, m_blk, n_blk);
             if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop, args.wait_cycles)) break;
             tc_fence_after();
             const uint32_t row = m_blk * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
             const bool row_ok = row < args.rows;
-            tile_epilogue<EPI>(args, lane_addr, row, row_ok, n_blk,
-                               bars + 256 + quarter * QKV_STAGE_BYTES, lane);
+            if (!item.split || split_tile_merge(args, item, lane_addr, quarter * 32 + lane, BM, 4, lane, stop))
+                tile_epilogue<EPI>(args, lane_addr, row, row_ok, n_blk,
+                                   bars + 256 + quarter * QKV_STAGE_BYTES, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
@@ -468,7 +572,7 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
 
-    const uint32_t total_tiles = args.tiles_m * args.tiles_n;     /* tiles_m counts 256-row tiles */
+    /* tiles_m counts 256-row tiles */
     const uint32_t group_tiles = args.group_m * args.tiles_n;
     auto tile_coords = [&](uint32_t tile, uint32_t &m_blk, uint32_t &n_blk) {
         uint32_t group = tile / group_tiles, local = tile % group_tiles;
@@ -483,14 +587,15 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool alive = true;
-            for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+            WorkItem item;
+            for (uint32_t pass = 0; alive && next_item(args, pair, pairs, pass, item); pass++) {
                 uint32_t m_blk, n_blk;
-                tile_coords(tile, m_blk, n_blk);
+                tile_coords(item.tile, m_blk, n_blk);
                 const int a_row = int(m_blk * 256 + rank * BM);
                 const int b_row = EPI == H3B_EPI_SWIGLU
                                       ? int((rank ? args.up_offset : 0u) + n_blk * 128)
                                       : int(n_blk * BN + rank * 128);
-                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                for (uint32_t kb = item.kb0; kb < item.kb1; kb++) {
                     if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, stop, args.wait_cycles)) { alive = false; break; }
                     const uint32_t bar = cluster_map(full_bar + 8 * stage, 0);
                     if (rank == 0) mbar_expect_tx(full_bar + 8 * stage, 2 * PAIR_STAGE_BYTES);
@@ -508,11 +613,12 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
-            for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+            WorkItem item;
+            for (uint32_t pass = 0; alive && next_item(args, pair, pairs, pass, item); pass++) {
                 if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8 * acc, acc_phase ^ 1, stop, args.wait_cycles))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < args.k_blocks; kb++) {
+                for (uint32_t kb = item.kb0; kb < item.kb1; kb++) {
                     if (!__all_sync(0xffffffffu, mbar_wait(full_bar + 8 * stage, phase, stop, args.wait_cycles))) {
                         alive = false;
                         break;
@@ -520,7 +626,7 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     tc_fence_after();
                     const uint32_t a_lo = a_lo0 + stage * (A_BYTES >> 4);
                     const uint32_t b_lo = b_lo0 + stage * ((B_BYTES / 2) >> 4);
-                    if (kb == 0) umma_ss_pair<false>(d_tmem, a_lo, b_lo, idesc, leader);
+                    if (kb == item.kb0) umma_ss_pair<false>(d_tmem, a_lo, b_lo, idesc, leader);
                     else umma_ss_pair<true>(d_tmem, a_lo, b_lo, idesc, leader);
 #pragma unroll
                     for (int k = 1; k < BK / 16; k++)
@@ -537,15 +643,18 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         /* ---- epilogue (both CTAs): warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ---- */
         const uint32_t quarter = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
-        for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
+        WorkItem item;
+        for (uint32_t pass = 0; next_item(args, pair, pairs, pass, item); pass++) {
             uint32_t m_blk, n_blk;
-            tile_coords(tile, m_blk, n_blk);
+            tile_coords(item.tile, m_blk, n_blk);
             if (!mbar_wait(acc_full + 8 * acc, acc_phase, stop, args.wait_cycles)) break;
             tc_fence_after();
             const uint32_t row = m_blk * 256 + rank * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
-            tile_epilogue<EPI>(args, lane_addr, row, row < args.rows, n_blk,
-                               bars + 256 + quarter * QKV_STAGE_BYTES, lane);
+            if (!item.split ||
+                split_tile_merge(args, item, lane_addr, rank * BM + quarter * 32 + lane, 2 * BM, 8, lane, stop))
+                tile_epilogue<EPI>(args, lane_addr, row, row < args.rows, n_blk,
+                                   bars + 256 + quarter * QKV_STAGE_BYTES, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(cluster_map(acc_empty + 8 * acc, 0));
@@ -707,6 +816,48 @@ int max_resident_pairs(int device) {
     return pairs;
 }
 
+/* Decides whether the last, partly filled round of tiles is split along K, and prepares the
+ * scratch for it. `workers` = tiles in flight (CTAs or CTA pairs), tile_rows = 128 or 256.
+ * Without the split a launch whose tile count is not a multiple of the workers pays a whole
+ * round for the leftover tiles (525 pair tiles on 74 pairs: 8 rounds for 7.1 rounds of work);
+ * with it the leftover tiles are shared by all workers. Returns false only on an allocation or
+ * memset failure. */
+bool configure_split(h3_gpu *gpu, TcArgs &args, uint32_t workers, uint32_t tile_rows) {
+    args.split_tiles = args.split = 0;
+    args.split_scratch = nullptr;
+    args.split_counters = nullptr;
+    const uint32_t total = args.tiles_m * args.tiles_n;
+    if (env_flag("H3B_NO_SPLIT_K") || total <= workers) return true;
+    const uint32_t leftover = total % workers;
+    if (!leftover) return true;
+    uint32_t split = workers / leftover;
+    if (split > args.k_blocks / 4) split = args.k_blocks / 4;     /* at least 4 K blocks per slice */
+    if (split > 16) split = 16;
+    if (split < 2) return true;
+    const size_t need = size_t(leftover) * (split - 1) * tile_rows * BN * sizeof(float);
+    if (need > h3_gpu::kSplitScratchBytes) return true;
+    if (!gpu->split_scratch) {
+        if (gpu->allocation_barred) return true;      /* a no-allocation entry point is running */
+        void *block = nullptr;
+        if (cudaMalloc(&block, h3_gpu::kSplitScratchBytes + h3_gpu::kSplitCounterBytes) != cudaSuccess) {
+            cudaGetLastError();
+            return true;                              /* no scratch: run without the split */
+        }
+        gpu->split_scratch = block;
+    }
+    uint32_t *counters = reinterpret_cast<uint32_t *>(static_cast<char *>(gpu->split_scratch) +
+                                                      h3_gpu::kSplitScratchBytes);
+    if (cudaMemsetAsync(counters, 0, size_t(leftover) * sizeof(uint32_t), gpu->stream) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    args.split_tiles = leftover;
+    args.split = split;
+    args.split_scratch = static_cast<float *>(gpu->split_scratch);
+    args.split_counters = counters;
+    return true;
+}
+
 template <int EPI>
 int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               const uint16_t *bias, uint32_t rows, uint32_t k, uint32_t weight_rows,
@@ -774,12 +925,14 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
         const uint32_t groups = (args.tiles_m + gm - 1) / gm;
         args.group_m = (args.tiles_m + groups - 1) / groups;
         const uint32_t tiles = args.tiles_m * args.tiles_n;
-        const uint32_t grid = 2 * (tiles < uint32_t(pairs) ? tiles : uint32_t(pairs));
-        h3b_gemm_pair<EPI><<<grid, TC_THREADS, pair_smem<EPI>(), gpu->stream>>>(map_a, map_b, args);
+        const uint32_t workers = tiles < uint32_t(pairs) ? tiles : uint32_t(pairs);
+        if (!configure_split(gpu, args, workers, 2 * BM)) return 0;
+        h3b_gemm_pair<EPI><<<2 * workers, TC_THREADS, pair_smem<EPI>(), gpu->stream>>>(map_a, map_b, args);
         return 1;
     }
     uint32_t tiles = args.tiles_m * args.tiles_n;
     uint32_t grid = tiles < uint32_t(gpu->sm_count) ? tiles : uint32_t(gpu->sm_count);
+    if (!configure_split(gpu, args, grid, BM)) return 0;
     h3b_gemm_tc<EPI><<<grid, TC_THREADS, smem_bytes, gpu->stream>>>(map_a, map_b, args);
     return 1;
 }

@@ -59,14 +59,17 @@ struct Vec8 {
     float v[8];
 };
 
-__device__ __forceinline__ Vec8 load8(const uint16_t *p) {
-    uint4 raw = *reinterpret_cast<const uint4 *>(p);
+__device__ __forceinline__ Vec8 unpack8(const uint4 raw) {
     Vec8 r;
     r.v[0] = h3b_lo(raw.x); r.v[1] = h3b_hi(raw.x);
     r.v[2] = h3b_lo(raw.y); r.v[3] = h3b_hi(raw.y);
     r.v[4] = h3b_lo(raw.z); r.v[5] = h3b_hi(raw.z);
     r.v[6] = h3b_lo(raw.w); r.v[7] = h3b_hi(raw.w);
     return r;
+}
+
+__device__ __forceinline__ Vec8 load8(const uint16_t *p) {
+    return unpack8(*reinterpret_cast<const uint4 *>(p));
 }
 
 __device__ __forceinline__ uint4 pack8(const Vec8 &x) {
@@ -456,42 +459,84 @@ __global__ void h3b_euler_kernel(float *sample, const uint16_t *last, const uint
     sample[i] = fmaf(delta, velocity, sample[i]);
 }
 
+/* Token pool / expand, unfused forms: VEC = 8 BF16 (one 16-byte vector) per thread when the
+ * width is a multiple of 8 and every view is 16-byte aligned, else one element per thread. The
+ * arithmetic per element is the reference's (h3_cuda_dit.cu:336-364). */
+template <int VEC>
 __global__ void h3b_token_pool_kernel(const uint16_t *input, const uint32_t *pairs, uint16_t *out,
                                       uint16_t *baseline, const uint32_t *baseline_indices,
                                       uint16_t *original, uint32_t rows, uint32_t width) {
+    const uint32_t per_row = width / VEC;
     size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= size_t(rows) * width) return;
-    uint32_t row = uint32_t(idx / width), col = uint32_t(idx % width);
-    uint32_t first = pairs[2 * row], second = pairs[2 * row + 1];
-    uint16_t lhs = input[size_t(first) * width + col];
-    original[size_t(first) * width + col] = lhs;
-    uint16_t pooled = lhs;
-    if (first != second) {
-        uint16_t rhs = input[size_t(second) * width + col];
-        original[size_t(second) * width + col] = rhs;
-        pooled = h3b_narrow((h3b_widen(lhs) + h3b_widen(rhs)) * 0.5f);
+    if (idx >= size_t(rows) * per_row) return;
+    const uint32_t row = uint32_t(idx / per_row), col = uint32_t(idx % per_row) * VEC;
+    const uint32_t first = pairs[2 * row], second = pairs[2 * row + 1];
+    const uint32_t b = baseline_indices[row];
+    const size_t at_first = size_t(first) * width + col, at_out = size_t(row) * width + col;
+    if (VEC == 8) {
+        const uint4 lhs = *reinterpret_cast<const uint4 *>(input + at_first);
+        *reinterpret_cast<uint4 *>(original + at_first) = lhs;
+        uint4 pooled = lhs;
+        if (first != second) {
+            const size_t at_second = size_t(second) * width + col;
+            const uint4 rhs = *reinterpret_cast<const uint4 *>(input + at_second);
+            *reinterpret_cast<uint4 *>(original + at_second) = rhs;
+            const Vec8 l = unpack8(lhs);
+            const Vec8 r = unpack8(rhs);
+            Vec8 y;
+#pragma unroll
+            for (int e = 0; e < 8; e++) y.v[e] = (l.v[e] + r.v[e]) * 0.5f;
+            pooled = pack8(y);
+        }
+        *reinterpret_cast<uint4 *>(out + at_out) = pooled;
+        if (b != kNoBaseline) *reinterpret_cast<uint4 *>(baseline + size_t(b) * width + col) = pooled;
+    } else {
+        const uint16_t lhs = input[at_first];
+        original[at_first] = lhs;
+        uint16_t pooled = lhs;
+        if (first != second) {
+            const uint16_t rhs = input[size_t(second) * width + col];
+            original[size_t(second) * width + col] = rhs;
+            pooled = h3b_narrow((h3b_widen(lhs) + h3b_widen(rhs)) * 0.5f);
+        }
+        out[at_out] = pooled;
+        if (b != kNoBaseline) baseline[size_t(b) * width + col] = pooled;
     }
-    out[idx] = pooled;
-    uint32_t b = baseline_indices[row];
-    if (b != kNoBaseline) baseline[size_t(b) * width + col] = pooled;
 }
 
+template <int VEC>
 __global__ void h3b_token_expand_kernel(const uint16_t *original, const uint16_t *reduced,
                                         const uint16_t *baseline,
                                         const uint32_t *baseline_indices, const uint32_t *parents,
                                         uint16_t *out, uint32_t rows, uint32_t width,
                                         uint32_t exact_prefix_rows, float update_scale) {
+    const uint32_t per_row = width / VEC;
     size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= size_t(rows) * width) return;
-    uint32_t row = uint32_t(idx / width), col = uint32_t(idx % width);
-    uint32_t parent = parents[row];
-    uint16_t value = reduced[size_t(parent) * width + col];
-    uint32_t b = baseline_indices[parent];
-    if (row >= exact_prefix_rows && b != kNoBaseline) {
-        float update = h3b_widen(value) - h3b_widen(baseline[size_t(b) * width + col]);
-        value = h3b_narrow(h3b_widen(original[idx]) + update_scale * update);
+    if (idx >= size_t(rows) * per_row) return;
+    const uint32_t row = uint32_t(idx / per_row), col = uint32_t(idx % per_row) * VEC;
+    const uint32_t parent = parents[row];
+    const uint32_t b = baseline_indices[parent];
+    const bool update = row >= exact_prefix_rows && b != kNoBaseline;
+    const size_t at = size_t(row) * width + col, at_parent = size_t(parent) * width + col;
+    if (VEC == 8) {
+        uint4 value = *reinterpret_cast<const uint4 *>(reduced + at_parent);
+        if (update) {
+            const Vec8 v = unpack8(value);
+            const Vec8 base = load8(baseline + size_t(b) * width + col), o = load8(original + at);
+            Vec8 y;
+#pragma unroll
+            for (int e = 0; e < 8; e++) y.v[e] = o.v[e] + update_scale * (v.v[e] - base.v[e]);
+            value = pack8(y);
+        }
+        *reinterpret_cast<uint4 *>(out + at) = value;
+    } else {
+        uint16_t value = reduced[at_parent];
+        if (update) {
+            const float delta = h3b_widen(value) - h3b_widen(baseline[size_t(b) * width + col]);
+            value = h3b_narrow(h3b_widen(original[at]) + update_scale * delta);
+        }
+        out[at] = value;
     }
-    out[idx] = value;
 }
 
 inline unsigned blocks_for(size_t items, int threads) {
@@ -803,9 +848,12 @@ extern "C" int h3x_adaln_linear_bf16_noalloc(h3_gpu *gpu, h3_gpu_tensor *output,
     launch_row<ROW_ADALN_KEEP>(gpu, a);
     if (!h3b_launched(gpu, "adaln_linear_bf16_noalloc normalisation")) return 0;
     if (!output_dim) return 1;
-    return h3b_gemm_bf16(gpu, h3b_ptr<uint16_t>(output), normed, h3b_ptr<uint16_t>(weight),
-                         bias ? h3b_ptr<uint16_t>(bias) : nullptr, rows, width, output_dim,
-                         H3B_EPI_STORE, "adaln_linear_bf16_noalloc");
+    gpu->allocation_barred = 1;       /* the projection must not create its split-tail scratch here */
+    const int done = h3b_gemm_bf16(gpu, h3b_ptr<uint16_t>(output), normed, h3b_ptr<uint16_t>(weight),
+                                   bias ? h3b_ptr<uint16_t>(bias) : nullptr, rows, width, output_dim,
+                                   H3B_EPI_STORE, "adaln_linear_bf16_noalloc");
+    gpu->allocation_barred = 0;
+    return done;
 }
 
 /* ----------------------------------------------------------- elementwise */
@@ -941,11 +989,15 @@ extern "C" int h3_gpu_token_pool_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
         !h3b_need(gpu, pairs, H3_GPU_U32, size_t(rows) * 2, "token pool pairs") ||
         !h3b_need_command(gpu))
         return 0;
-    h3b_token_pool_kernel<<<blocks_for(count, 256), 256, 0, gpu->stream>>>(
-        h3b_ptr<uint16_t>(input, input_offset), h3b_ptr<uint32_t>(pairs),
-        h3b_ptr<uint16_t>(output), h3b_ptr<uint16_t>(baseline, baseline_offset),
-        h3b_ptr<uint32_t>(baseline_indices), h3b_ptr<uint16_t>(original, original_offset), rows,
-        width);
+    const uint16_t *in = h3b_ptr<uint16_t>(input, input_offset);
+    uint16_t *out = h3b_ptr<uint16_t>(output), *base = h3b_ptr<uint16_t>(baseline, baseline_offset);
+    uint16_t *orig = h3b_ptr<uint16_t>(original, original_offset);
+    if (width % 8 == 0 && all_aligned16({in, out, base, orig}))
+        h3b_token_pool_kernel<8><<<blocks_for(count / 8, 256), 256, 0, gpu->stream>>>(
+            in, h3b_ptr<uint32_t>(pairs), out, base, h3b_ptr<uint32_t>(baseline_indices), orig, rows, width);
+    else
+        h3b_token_pool_kernel<1><<<blocks_for(count, 256), 256, 0, gpu->stream>>>(
+            in, h3b_ptr<uint32_t>(pairs), out, base, h3b_ptr<uint32_t>(baseline_indices), orig, rows, width);
     return h3b_launched(gpu, "token_pool_bf16");
 }
 
@@ -1014,11 +1066,17 @@ extern "C" int h3_gpu_token_expand_delta_bf16(
         !h3b_need(gpu, parents, H3_GPU_U32, rows, "token expand parents") ||
         !h3b_need_command(gpu))
         return 0;
-    h3b_token_expand_kernel<<<blocks_for(count, 256), 256, 0, gpu->stream>>>(
-        h3b_ptr<uint16_t>(original, original_offset), h3b_ptr<uint16_t>(reduced),
-        h3b_ptr<uint16_t>(baseline, baseline_offset), h3b_ptr<uint32_t>(baseline_indices),
-        h3b_ptr<uint32_t>(parents), h3b_ptr<uint16_t>(output), rows, width, exact_prefix_rows,
-        update_scale);
+    const uint16_t *orig = h3b_ptr<uint16_t>(original, original_offset);
+    const uint16_t *red = h3b_ptr<uint16_t>(reduced), *base = h3b_ptr<uint16_t>(baseline, baseline_offset);
+    uint16_t *out = h3b_ptr<uint16_t>(output);
+    if (width % 8 == 0 && all_aligned16({orig, red, base, out}))
+        h3b_token_expand_kernel<8><<<blocks_for(count / 8, 256), 256, 0, gpu->stream>>>(
+            orig, red, base, h3b_ptr<uint32_t>(baseline_indices), h3b_ptr<uint32_t>(parents), out, rows,
+            width, exact_prefix_rows, update_scale);
+    else
+        h3b_token_expand_kernel<1><<<blocks_for(count, 256), 256, 0, gpu->stream>>>(
+            orig, red, base, h3b_ptr<uint32_t>(baseline_indices), h3b_ptr<uint32_t>(parents), out, rows,
+            width, exact_prefix_rows, update_scale);
     return h3b_launched(gpu, "token_expand_delta_bf16");
 }
 

@@ -146,6 +146,61 @@ def test_file_loads_and_streaming(gpu, pkg, tmp_path):
     assert err.value
 
 
+@pytest.mark.parametrize("direct", ["1", "0"])
+def test_large_file_loads_cross_chunk_boundaries(pkg, tmp_path, monkeypatch, direct):
+    """A payload of several 16 MiB chunks at an odd byte offset: the chunked, multi-threaded
+    reader (with and without O_DIRECT) must deliver every byte in place, also when the ring of
+    staging buffers wraps (more chunks than buffers) and when the tensor is filled twice."""
+    monkeypatch.setenv("H3B_DIRECT_IO", direct)
+    rng = np.random.default_rng(3)
+    elements = (120 << 20) // 2 + 12345                     # ~120 MiB of BF16: 8 chunks > 6 buffers
+    payload = rng.integers(0, 1 << 16, elements, dtype=np.uint16)
+    path = tmp_path / "big.bin"
+    with open(path, "wb") as f:
+        f.write(b"h" * 4099)                                # payload starts off the 4 KiB grid
+        f.write(payload.tobytes())
+        f.write(b"t" * 100)
+    g = pkg.Gpu(0)
+    try:
+        lib, p = g.lib, str(path).encode()
+        h = lib.h3_gpu_tensor_load_bf16(g.handle, p, 4099, elements)
+        assert h, g.error()
+        t = pkg.Tensor(g, h, elements, pkg.BF16)
+        assert np.array_equal(t.read(), payload)
+        err = C.create_string_buffer(256)
+        # a window in the middle, into the same tensor, through the streaming entry point
+        assert lib.h3_gpu_tensor_stream_file_bf16(t.handle, p, 4099 + 2 * 1000001, 20_000_000, err, 256) == 1
+        assert np.array_equal(t.read(20_000_000), payload[1000001:21000001])
+        assert lib.h3_gpu_tensor_read_file_bf16(t.handle, p, 4099, elements + 100, err, 256) == 0
+    finally:
+        g.close()
+
+
+def test_op_profile_prints_device_time_per_op(pkg, monkeypatch, capfd):
+    """H3_PROFILE=2: h3_gpu_profile_mark prints, per op name, the device time measured with
+    events on the context's stream (the reference prints wall/wait per phase only,
+    h3_gpu_cuda.cu:21-45,919-933)."""
+    monkeypatch.setenv("H3_PROFILE", "2")
+    g = pkg.Gpu(0)
+    try:
+        a = g.bf16(o.normal_bf16(1 << 16, 1))
+        out = g.new(1 << 16, pkg.BF16)
+        g.begin()
+        for _ in range(3):
+            g.op("add_bf16", out, a, a, 1 << 16)
+        g.op("silu_bf16", out, a, 1 << 16)
+        g.submit()
+        g.lib.h3_gpu_profile_set_label(g.handle, b"probe")
+        g.lib.h3_gpu_profile_mark(g.handle, b"elementwise")
+    finally:
+        g.close()
+    err = capfd.readouterr().err
+    assert "[probe] elementwise" in err
+    rows = [line for line in err.splitlines() if "launches" in line]
+    assert any("add_bf16" in r and " 3 launches" in r for r in rows), err
+    assert any("silu_bf16" in r and " 1 launches" in r for r in rows), err
+
+
 def test_entry_points_off_the_dit_path_fail_with_a_message(gpu, pkg):
     """The reference's practice for unported ops: return 0 and say so (h3_cuda_dit.cu:1072-1216)."""
     lib = gpu.lib

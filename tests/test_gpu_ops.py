@@ -393,6 +393,67 @@ def test_grouped_qkv_linear_rope(gpu, pkg, monkeypatch, rows, k, heads, unfused)
     assert_gemm_close(tv.read(), v, "v")
 
 
+@pytest.mark.parametrize("kernel", ["pairs", "lone"])
+def test_split_tail_round_of_the_tensor_core_gemm(gpu, pkg, monkeypatch, kernel):
+    """Tile counts that leave a partly filled last round: the leftover tiles are split along K
+    over all CTAs (F32 partial tiles, fixed-order merge, then the usual epilogue). Covered for
+    the plain, SwiGLU and QKV epilogues on CTA pairs (256 x 256 tiles, 74 pairs) and on lone
+    CTAs (128 x 256 tiles, 148 CTAs), against the oracle and against the same launch with the
+    split switched off."""
+    if kernel == "lone":
+        monkeypatch.setenv("H3B_NO_CTA_PAIRS", "1")
+    rows = 512 if kernel == "pairs" else 384          # 2 pair row tiles / 3 lone row tiles
+    col_tiles = 38 if kernel == "pairs" else 50       # 76 pair tiles on 74 pairs / 150 tiles on 148 CTAs
+    k = 1024                                          # 16 K blocks: slices of 4
+    results = {}
+    for split in ("1", "0"):
+        monkeypatch.setenv("H3B_NO_SPLIT_K", "0" if split == "1" else "1")
+        # plain projection + bias
+        n = col_tiles * 256 - 40                      # ragged last column tile
+        x, w, b = bf(rows * k, 1), bf(n * k, 2, 1.0 / np.sqrt(k)), bf(n, 3)
+        tx, tw, tb, out = gpu.bf16(x), gpu.bf16(w), gpu.bf16(b), gpu.new(rows * n, pkg.BF16)
+        run(gpu, lambda: gpu.op("linear_bf16", out, tx, tw, tb, rows, k, n))
+        results["linear", split] = out.read()
+        if split == "1":
+            assert_gemm_close(results["linear", split], o.linear_bf16(x, w, b, rows, k, n), "split linear")
+        # fc1 + SwiGLU (a column tile = 128 gate + 128 up columns)
+        hidden = col_tiles * 128
+        fc1 = bf(2 * hidden * k, 4, 1.0 / np.sqrt(k))
+        t1, act = gpu.bf16(fc1), gpu.new(rows * hidden, pkg.BF16)
+        run(gpu, lambda: gpu.op("h3x_linear_swiglu_bf16", act, tx, t1, rows, k, hidden))
+        results["swiglu", split] = act.read()
+        if split == "1":
+            fused = o.linear_bf16(x, fc1, None, rows, k, 2 * hidden)
+            assert_aggregate_close(results["swiglu", split], o.swiglu_bf16(fused, rows, hidden), "split swiglu")
+        # QKV + head norm + RoPE (a column tile = two 128-column units)
+        heads = (col_tiles * 2 - 1) // 3              # 25 / 33 heads: 75 / 99 units, last tile half empty
+        wq = bf(3 * heads * 128 * k, 5, 1.0 / np.sqrt(k))
+        qw, kw, cos, sin = bf(128, 6, 0.5), bf(128, 7, 0.5), bf(rows * 48, 8), bf(rows * 48, 9)
+        cnt = rows * heads * 128
+        tq, tk, tv = (gpu.new(cnt, pkg.BF16) for _ in range(3))
+        scratch = gpu.new(3 * cnt, pkg.BF16)
+        t = [gpu.bf16(a) for a in (wq, qw, kw, cos, sin)]
+        run(gpu, lambda: gpu.op("grouped_qkv_linear_rope_bf16", tq, tk, tv, scratch, tx, *t, rows, k, heads,
+                                128, 48, 1e-5))
+        results["qkv", split] = np.concatenate([tq.read(), tk.read(), tv.read()])
+        if split == "1":
+            qkv = o.linear_bf16(x, wq, None, rows, k, 3 * heads * 128)
+            q, kk, v = o.qkv_rope_bf16(qkv, qw, kw, cos, sin, rows, heads, 128, 48, 1)
+            assert_aggregate_close(tq.read(), q, "split q", rel_l2=3e-3, max_abs=5e-2)
+            assert_aggregate_close(tk.read(), kk, "split k", rel_l2=3e-3, max_abs=5e-2)
+            assert_gemm_close(tv.read(), v, "split v")
+    assert lib_status(gpu) == 0
+    for name in ("linear", "swiglu", "qkv"):
+        # the split changes the order of the F32 sum for the split tiles only: isolated last-bit moves
+        a, b_ = results[name, "1"], results[name, "0"]
+        assert_aggregate_close(a, b_, f"{name}: split vs whole", rel_l2=2e-3, max_abs=5e-2)
+        assert np.mean(a != b_) < 0.05
+
+
+def lib_status(gpu):
+    return gpu.lib.h3x_kernel_status(gpu.handle)
+
+
 def test_ulysses_pack_unpack_roundtrip(gpu, pkg):
     rows, heads, hd, world = 37, 8, 128, 4
     x = bf(rows * heads * hd, 1)
