@@ -62,6 +62,7 @@ struct h3_gpu {
     static constexpr size_t kSplitScratchBytes = size_t(40) << 20;
     static constexpr size_t kSplitCounterBytes = 4096;
     void *split_scratch = nullptr;
+    int split_counters_dirty = 1;   /* the counter words must be cleared before the next split launch */
     int allocation_barred = 0;      /* set while an entry point that must not allocate runs */
 
     /* exact-size cache of freed device blocks; reuse is ordered by the stream */

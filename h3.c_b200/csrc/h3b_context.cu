@@ -352,6 +352,7 @@ extern "C" int h3_gpu_submit(h3_gpu *gpu) {
     if (kernel_status != H3B_STATUS_OK) {
         cudaMemsetAsync(gpu->status_device, 0, sizeof(int), gpu->stream);
         gpu->status_seen = kernel_status;
+        gpu->split_counters_dirty = 1;      /* a GEMM that gave up may have left its counters half-way */
         if (kernel_status == H3B_STATUS_PEER_TIMEOUT)
             return h3b_fail(gpu, "a peer barrier gave up waiting for another rank (status %d)",
                             kernel_status);

@@ -75,7 +75,7 @@ struct TcArgs {
      * its accumulator in a fixed order and runs the epilogue. split_tiles == 0: off. */
     uint32_t split_tiles, split;
     float *split_scratch;         /* [split_tiles][split - 1][tile rows][256] */
-    uint32_t *split_counters;     /* [split_tiles], zeroed before the launch */
+    uint32_t *split_counters;     /* [2][split_tiles]: partials delivered, finishing warps done */
     uint32_t up_offset;   /* SwiGLU: weight row of the first up column (= hidden) */
     /* QKV + norm + RoPE epilogue */
     uint16_t *q_out, *k_out, *v_out;
@@ -207,16 +207,31 @@ __device__ __forceinline__ bool next_item(const TcArgs &args, uint32_t worker, u
 /* Epilogue side of a split tile for one thread (= one accumulator row). row_in_tile: the row's
  * index inside the tile; tile_rows: 128 (lone CTA) or 256 (CTA pair); arrivals: epilogue warps
  * per worker (4 or 8). Returns true when this thread goes on to the normal epilogue (its
- * accumulator now holds the whole sum), false when it only delivered a partial or gave up. */
-__device__ __forceinline__ bool split_tile_merge(const TcArgs &args, const WorkItem &item,
-                                                 uint32_t lane_addr, uint32_t row_in_tile,
-                                                 uint32_t tile_rows, uint32_t arrivals, uint32_t lane,
-                                                 volatile int *stop) {
-    const size_t tile_floats = size_t(tile_rows) * BN;
-    float *slot_base = args.split_scratch + size_t(item.slot) * (args.split - 1) * tile_floats;
-    uint32_t *counter = args.split_counters + item.slot;
-    if (item.part != 0) {
-        float *dst = slot_base + size_t(item.part - 1) * tile_floats + size_t(row_in_tile) * BN;
+ * accumulator now holds the whole sum), false when it only delivered a partial or gave up.
+ * A partial tile is stored as [32-column chunk][16-byte vector of the chunk][row][4 floats], so
+ * the 32 threads of a warp (32 consecutive rows) write and read 512 contiguous bytes per
+ * instruction although each of them owns a row. Counters: [slot] counts delivered partials,
+ * [split_tiles + slot] counts finishing warps that are done; the last of those clears both,
+ * so the words are zero again when the kernel ends. */
+constexpr uint32_t kMaxSplit = 4;     /* K slices per split tile, at most */
+
+struct SplitCall {     /* passed by value: the kernel's argument block stays in constant memory */
+    float *scratch;
+    uint32_t *counters;
+    long long wait_cycles;
+    uint32_t split_tiles, split, slot, part;
+};
+
+__device__ __noinline__ bool split_tile_merge(const SplitCall args, uint32_t lane_addr,
+                                              uint32_t row_in_tile, uint32_t tile_rows,
+                                              uint32_t arrivals, uint32_t lane, volatile int *stop) {
+    const size_t tile_vectors = size_t(tile_rows) * (BN / 4);
+    uint4 *slot_base = reinterpret_cast<uint4 *>(args.scratch) +
+                       size_t(args.slot) * (args.split - 1) * tile_vectors;
+    uint32_t *delivered = args.counters + args.slot;
+    uint32_t *finished = args.counters + args.split_tiles + args.slot;
+    if (args.part != 0) {
+        uint4 *dst = slot_base + size_t(args.part - 1) * tile_vectors + row_in_tile;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; c++) {
             uint32_t r[32];
@@ -224,12 +239,12 @@ __device__ __forceinline__ bool split_tile_merge(const TcArgs &args, const WorkI
             tmem_ld_wait();
 #pragma unroll
             for (int v = 0; v < 8; v++)
-                __stcg(reinterpret_cast<uint4 *>(dst + c * 32) + v,
+                __stcg(dst + size_t(c * 8 + v) * tile_rows,
                        make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
         }
         __threadfence();
         __syncwarp();
-        if (lane == 0) atomicAdd(counter, 1u);
+        if (lane == 0) atomicAdd(delivered, 1u);
         return false;
     }
     /* the finishing slice: wait for the other slices' partial tiles (bounded) */
@@ -239,37 +254,53 @@ __device__ __forceinline__ bool split_tile_merge(const TcArgs &args, const WorkI
         const long long start = clock64();
         for (;;) {
             uint32_t seen;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(delivered) : "memory");
             if (seen >= want) break;
             if (*stop || clock64() - start > args.wait_cycles) {
                 *stop = 1;
                 ok = 0;
                 break;
             }
-            __nanosleep(64);
+            __nanosleep(32);
         }
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) return false;
+    /* all partials of a 32-column chunk are requested at once (split <= kMaxSplit, so at most
+     * 24 vectors in flight per thread): one round trip to L2 per chunk, not one per partial */
 #pragma unroll 1
     for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
         tmem_ld32(lane_addr + c * 32, r);
-        tmem_ld_wait();
-        for (uint32_t part = 1; part < args.split; part++) {
-            const float *src = slot_base + size_t(part - 1) * tile_floats + size_t(row_in_tile) * BN + c * 32;
+        const uint4 *src = slot_base + size_t(c * 8) * tile_rows + row_in_tile;
+        uint4 p[kMaxSplit - 1][8];
 #pragma unroll
-            for (int v = 0; v < 8; v++) {
-                const uint4 p = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
-                r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + __uint_as_float(p.x));
-                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + __uint_as_float(p.y));
-                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + __uint_as_float(p.z));
-                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + __uint_as_float(p.w));
+        for (uint32_t part = 0; part < kMaxSplit - 1; part++)
+            if (part + 1 < args.split) {
+#pragma unroll
+                for (int v = 0; v < 8; v++)
+                    p[part][v] = __ldcg(src + size_t(part) * tile_vectors + size_t(v) * tile_rows);
             }
-        }
+        tmem_ld_wait();
+#pragma unroll
+        for (uint32_t part = 0; part < kMaxSplit - 1; part++)
+            if (part + 1 < args.split) {      /* fixed order: slice 1, 2, 3 */
+#pragma unroll
+                for (int v = 0; v < 8; v++) {
+                    r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + __uint_as_float(p[part][v].x));
+                    r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + __uint_as_float(p[part][v].y));
+                    r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + __uint_as_float(p[part][v].z));
+                    r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + __uint_as_float(p[part][v].w));
+                }
+            }
         tmem_st32(lane_addr + c * 32, r);
     }
     tmem_st_wait_all();
+    __syncwarp();
+    if (lane == 0 && atomicAdd(finished, 1u) == arrivals - 1) {
+        *finished = 0;
+        *delivered = 0;
+    }
     return true;
 }
 
@@ -484,7 +515,10 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t row = m_blk * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
             const bool row_ok = row < args.rows;
-            if (!item.split || split_tile_merge(args, item, lane_addr, quarter * 32 + lane, BM, 4, lane, stop))
+            if (!item.split ||
+                split_tile_merge(SplitCall{args.split_scratch, args.split_counters, args.wait_cycles,
+                                           args.split_tiles, args.split, item.slot, item.part},
+                                 lane_addr, quarter * 32 + lane, BM, 4, lane, stop))
                 tile_epilogue<EPI>(args, lane_addr, row, row_ok, n_blk,
                                    bars + 256 + quarter * QKV_STAGE_BYTES, lane);
             tc_fence_before();
@@ -652,7 +686,9 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const uint32_t row = m_blk * 256 + rank * BM + quarter * 32 + lane;
             const uint32_t lane_addr = tmem_base + acc * BN + ((quarter * 32) << 16);
             if (!item.split ||
-                split_tile_merge(args, item, lane_addr, rank * BM + quarter * 32 + lane, 2 * BM, 8, lane, stop))
+                split_tile_merge(SplitCall{args.split_scratch, args.split_counters, args.wait_cycles,
+                                           args.split_tiles, args.split, item.slot, item.part},
+                                 lane_addr, rank * BM + quarter * 32 + lane, 2 * BM, 8, lane, stop))
                 tile_epilogue<EPI>(args, lane_addr, row, row < args.rows, n_blk,
                                    bars + 256 + quarter * QKV_STAGE_BYTES, lane);
             tc_fence_before();
@@ -831,8 +867,8 @@ bool configure_split(h3_gpu *gpu, TcArgs &args, uint32_t workers, uint32_t tile_
     const uint32_t leftover = total % workers;
     if (!leftover) return true;
     uint32_t split = workers / leftover;
-    if (split > args.k_blocks / 4) split = args.k_blocks / 4;     /* at least 4 K blocks per slice */
-    if (split > 16) split = 16;
+    if (split > args.k_blocks / 8) split = args.k_blocks / 8;     /* at least 8 K blocks per slice */
+    if (split > kMaxSplit) split = kMaxSplit;     /* more slices shorten the round little and add partial tiles to merge */
     if (split < 2) return true;
     const size_t need = size_t(leftover) * (split - 1) * tile_rows * BN * sizeof(float);
     if (need > h3_gpu::kSplitScratchBytes) return true;
@@ -847,9 +883,14 @@ bool configure_split(h3_gpu *gpu, TcArgs &args, uint32_t workers, uint32_t tile_
     }
     uint32_t *counters = reinterpret_cast<uint32_t *>(static_cast<char *>(gpu->split_scratch) +
                                                       h3_gpu::kSplitScratchBytes);
-    if (cudaMemsetAsync(counters, 0, size_t(leftover) * sizeof(uint32_t), gpu->stream) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
+    /* the kernels leave the counters at zero; they are cleared here only for the first launch
+     * and after a launch that gave up on a wait */
+    if (gpu->split_counters_dirty) {
+        if (cudaMemsetAsync(counters, 0, h3_gpu::kSplitCounterBytes, gpu->stream) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        gpu->split_counters_dirty = 0;
     }
     args.split_tiles = leftover;
     args.split = split;
