@@ -49,11 +49,12 @@ WORKLOADS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel from an ncu
-# capture of this file's default command; (workload, ranks) -> bytes. Empty until a capture of
-# the current tile walk exists: the line then carries "traffic": null.
-NCU_DRAM_BYTES_PER_LAUNCH = {}
-NCU_DRAM_SOURCE = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel (fc1 + SwiGLU)
+# from an ncu capture of this file with --blocks 1; (workload, ranks) -> bytes. Configurations
+# without a capture report "traffic": null. To be re-captured whenever the GEMM tile walk changes.
+NCU_DRAM_BYTES_PER_LAUNCH = {("c3", 1): 1148.4e6}
+NCU_DRAM_SOURCE = ("one ncu capture of `bench.py --blocks 1` on a B200 (dram read 970.3 MB + write 178.1 MB for "
+                   "the fc1 + SwiGLU launch; summary in profiles/h3b_gemm_dram_traffic_c3.md)")
 
 
 def measured_peaks():
@@ -445,9 +446,19 @@ def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, rounds=3, re
                    (("qkv", 3 * s.inner * s.hidden), ("out", s.hidden * s.inner),
                     ("fc1", 2 * s.ffn * s.hidden), ("fc2", s.hidden * s.ffn))}
         q, k, v = (copy(t, rows * s.inner) for t in (dit.query, dit.key, dit.value))
+        norms = [copy(w.q_norm, s.head_dim), copy(w.k_norm, s.head_dim)]
+        ropes = [copy(step.rope_cos, rows * s.rope_half), copy(step.rope_sin, rows * s.rope_half)]
+        rq, rk, rv = (ref.new(rows * s.inner, pkg.BF16) for _ in range(3))
         theirs = {
-            "qkv_proj_norm_rope": lambda: ref.op("linear_bf16", wide, x, weights["qkv"], None, rows,
-                                                 s.hidden, 3 * s.inner),
+            # like for like: its projection followed by its norm + RoPE kernel, as its host calls it
+            "qkv_proj_norm_rope": lambda: ref.op("grouped_qkv_linear_rope_bf16", rq, rk, rv, wide, x,
+                                                 weights["qkv"], *norms, *ropes, rows, s.hidden,
+                                                 s.heads, s.head_dim, s.rope_half, s.eps),
+            "qkv_gemm_only": lambda: ref.op("linear_bf16", wide, x, weights["qkv"], None, rows,
+                                            s.hidden, 3 * s.inner),
+            # its whole MLP (two cuBLASLt GEMMs + a SwiGLU pass) against this library's two launches
+            "mlp_fc1_swiglu_fc2": lambda: ref.op("mlp_bf16", narrow, x, weights["fc1"], weights["fc2"],
+                                                 rows, s.hidden, s.ffn, s.hidden),
             "mlp_fc1_swiglu": lambda: ref.op("linear_bf16", wide, x, weights["fc1"], None, rows,
                                              s.hidden, 2 * s.ffn),
             "mlp_fc2": lambda: ref.op("linear_bf16", narrow, act, weights["fc2"], None, rows, s.ffn,
@@ -464,6 +475,8 @@ def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, rounds=3, re
                 s.head_dim, s.rope_half, s.eps),
             "mlp_fc1_swiglu": lambda: gpu.op("h3x_linear_swiglu_bf16", dit.qkv, dit.mod_attention, w.fc1,
                                              rows, s.hidden, s.ffn),
+            "mlp_fc1_swiglu_fc2": lambda: gpu.op("mlp_bf16", dit.attention_output, dit.mod_attention, w.fc1,
+                                                 w.fc2, rows, s.hidden, s.ffn, s.hidden),
             "mlp_fc2": lambda: gpu.op("linear_bf16", dit.attention_output, dit.qkv, w.fc2, None, rows,
                                       s.ffn, s.hidden),
             "gemm_out_proj": lambda: gpu.op("linear_bf16", dit.attention_output, dit.attention_heads,
@@ -471,6 +484,7 @@ def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, rounds=3, re
             "attention": lambda: gpu.op("sdpa_bf16", dit.attention_heads, dit.query, dit.key, dit.value,
                                         sequence, s.heads, s.head_dim, s.scale),
         }
+        ours["qkv_gemm_only"] = ours["qkv_proj_norm_rope"]     # this library has no unfused form to time
         out = {}
         for name in theirs:
             a, b = [], []
@@ -478,6 +492,8 @@ def reference_cuda_ops(torch, pkg, gpu, shape, dit, step, sequence, rounds=3, re
                 a.append(time_kernel(torch, gpu, ours[name], 0.0, repeats)[0])
                 b.append(time_kernel(torch, ref, theirs[name], 0.0, repeats)[0])
             out[name] = {"ms": statistics.mean(a), "reference_cuda_ms": statistics.mean(b)}
+        out["qkv_gemm_only"]["note"] = ("reference: the cuBLASLt projection alone; ms: this library's fused "
+                                        "projection + head norm + RoPE launch")
         return out
     except Exception as err:                      # a supplementary figure must not sink the run
         return {"unavailable": str(err)[:200]}
@@ -651,12 +667,14 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         io.host_velocity.copy_(io.velocity, non_blocking=True)   # D2H of the step's result
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        one_step()
+    # the clock sampler starts before the warm-up steps: its start-up (NVML initialisation in the
+    # child process) must not fall into the timed region
     sampler = ClockSampler(local_rank)
-    barrier()
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        one_step()
+    barrier()
     before = gpu.stats()
     ms_local = timed(one_step, args.steps, 0)
     after = gpu.stats()
@@ -727,6 +745,8 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         kernel_lines = {k: kernel_entry(k, v) for k, v in kernels.items()}
         if ref_ops and "unavailable" in ref_ops:
             kernel_lines["reference_cuda"] = ref_ops
+        elif ref_ops:
+            kernel_lines["paired_only"] = {k: v for k, v in ref_ops.items() if k not in kernels}
         kernel_lines["adaln_projection"] = {
             "ms": a12_ms, "gbs": a12_tbs * 1e3, "frac_of_hbm_peak": a12_tbs * 1e3 / peaks["hbm_gbs"],
             "bytes_per_launch": a12_bytes, "shape": f"{a12_rows} x {s.time_dim} -> {mod_cols} (+bias)"}
