@@ -2,7 +2,10 @@
  * attention. Replaces the reference's h3_cuda_attention.cu for the DiT path
  * behind the same C ABI.
  *
- * Flash attention on the 5th-generation tensor cores (head_dim 128):
+ * Flash attention on the 5th-generation tensor cores (head_dim 128), two kernels. Dense calls
+ * take h3b_sdpa_tc2 (described at its definition below: one 128-row query tile per CTA, three
+ * score buffers, softmax groups alternating over key steps); calls under a block-sparse mask, and
+ * dense calls with H3B_SDPA_TWO_TILES=1, take h3b_sdpa_tc:
  *   grid = (ceil(S/256), heads); one CTA per SM works on two 128-row query tiles that
  *   ping-pong: while one tile's softmax runs, the tensor core works for the other, and every
  *   K/V tile fetched into shared memory is used by both.
@@ -35,6 +38,7 @@
 #include "h3b_sm100.cuh"
 
 #include <cmath>
+#include <type_traits>
 #include <cstdlib>
 
 namespace {
@@ -748,6 +752,429 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     }
 }
 
+/* ------------------------------------------------------------------------------------------
+ * Second form of the tensor-core kernel: ONE 128-row query tile per CTA, THREE score buffers, and
+ * two softmax groups that alternate over the KEY steps of the tile.
+ *
+ *   tensor memory   S[0] | S[1] | S[2] | O  = 3 x 128 + 128 columns (all 512): the scores of step j
+ *                   go to S[j % 3]; P(j) (BF16 pairs, 64 columns) overwrites the first half of the
+ *                   buffer it came from and is the A operand of O += P(j).V(j).
+ *   MMA warp        per step j: O += P(j).V(j), then S[j % 3] = Q.K(j+3)^T into the buffer P(j) was
+ *                   just read from (the in-order pipe keeps the two apart). Scores are thus
+ *                   three steps ahead of the P.V products: a group that publishes P(j) finds the
+ *                   scores of its next step j+2 complete, and no MMA sits in the chain between
+ *                   two softmax passes of a group.
+ *   softmax         2 groups x 4 warps; a thread owns one query row (its TMEM lane) and all 128
+ *                   keys of a step; group g takes the steps j = g, g+2, ... There is no exchange
+ *                   inside a row. The two threads that share a row (one per group) hand the
+ *                   row's reference maximum back and forth through shared memory: the group of
+ *                   step j decides (lazily, threshold 2^8) whether to raise it, rescales O if so
+ *                   (after P(j-1).V(j-1) has completed), publishes it and signals the other
+ *                   group, whose step j+1 waits for that signal before its own decision. Each
+ *                   group keeps its own partial row sum, rescaled whenever it sees a new
+ *                   reference; the two are combined at the end.
+ *   ring            three stages; stage j % 3 holds what step j of the MMA warp reads, K(j+3) and
+ *                   V(j). They also die together: S(j+3) complete means Q.K(j+3)^T is done and,
+ *                   issued before it, so is P(j).V(j); a softmax thread that sees those scores
+ *                   releases the stage. One barrier per step ("go") collects everything the MMA
+ *                   warp waits for: the bytes of the two tiles and the four softmax warps'
+ *                   arrivals for P(j). The first three K tiles come with Q.
+ * The two-tile kernel above has QK^T -> softmax -> P.V as the serial chain of a tile's step;
+ * here nothing of a step waits for another unit's work on the same step but P.V for P. Measured
+ * (B200, CUDA events, S = 6,400 x 56 heads / S = 50,476 x 7 heads): 0.97 / 7.1 ms against
+ * 1.02-1.08 / 8.4 ms for the two-tile kernel, and with 7 heads at S = 6,400 (a rank's share
+ * under 8-way sequence parallelism, twice as many CTAs) 0.175 against 0.25 ms. What bounds a
+ * step now is shared-memory traffic: Q and K tiles are read by the tensor core for every MMA
+ * (64 KiB per step), V (32 KiB), and TMA writes the next K and V (64 KiB), 160 KiB at 128 bytes
+ * per cycle = 1,250 of the ~1,850 cycles a step takes; the two-tile kernel shares K and V between
+ * its tiles (128 KiB per tile step) but pays the serial chain. All waits are mbarrier waits with
+ * the context's budget (no named barriers: a group that gives up can never leave the other one
+ * blocked). Dense attention only; the block-sparse mask keeps the two-tile kernel. */
+constexpr int A2_QT = 128, A2_KV = 128, A2_D = 128;
+constexpr int A2_STAGES = 3, A2_S_BUFFERS = 3;
+constexpr int A2_THREADS = 64 + 32 * 8;                    /* producer, MMA, 2 groups x 4 softmax warps */
+constexpr int A2_TILE_BYTES = A2_KV * A2_D * 2;             /* 32 KiB: Q tile, K stage, V stage */
+constexpr int A2_BAR_BYTES = 512;
+constexpr int A2_STATE_BYTES = 5 * A2_QT * 4;   /* per row: reference maximum; (sum, its reference) per group */
+constexpr size_t A2_SMEM = size_t(1 + 2 * A2_STAGES) * A2_TILE_BYTES + A2_BAR_BYTES +
+                           A2_STATE_BYTES;
+static_assert(A2_SMEM <= 232448, "the step-alternating attention kernel needs at most 227 KiB of shared memory");
+constexpr uint32_t A2_COL_S = 0, A2_COL_O = A2_S_BUFFERS * A2_KV;
+
+template <bool PUSH>
+__global__ void __launch_bounds__(A2_THREADS, 1)
+h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+             const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
+    extern __shared__ __align__(1024) uint8_t at_smem[];
+    const uint32_t base = smem_u32(at_smem);
+    const uint32_t q_smem = base;
+    const uint32_t k_smem = q_smem + A2_TILE_BYTES;
+    const uint32_t v_smem = k_smem + A2_STAGES * A2_TILE_BYTES;
+    const uint32_t bars = v_smem + A2_STAGES * A2_TILE_BYTES;
+    const uint32_t q_full = bars;                              /* 1                    */
+    const uint32_t go = q_full + 8;                            /* [stage] = 3: tiles loaded and P published */
+    const uint32_t stage_free = go + 8 * A2_STAGES;            /* [stage] = 3          */
+    const uint32_t s_full = stage_free + 8 * A2_STAGES;        /* [buffer] = 3         */
+    const uint32_t pv_tail = s_full + 8 * A2_S_BUFFERS;        /* [step parity] = 2    */
+    const uint32_t ref_bar = pv_tail + 16;                     /* [deciding group][quarter] = 8 */
+    const uint32_t o_done = ref_bar + 64;                      /* 1                    */
+    const uint32_t sum_bar = o_done + 8;                       /* [quarter] = 4        */
+    const uint32_t out_bar = sum_bar + 32;                     /* [quarter] = 4        */
+    const uint32_t tmem_holder = out_bar + 32;
+    volatile int *stop = reinterpret_cast<volatile int *>(at_smem + (tmem_holder + 8 - base));
+    float *state = reinterpret_cast<float *>(at_smem + (bars - base) + A2_BAR_BYTES);
+    float *row_reference = state;                              /* [128]: reference maximum (log2 units) */
+    float *group_sum = state + A2_QT;                          /* [2][128] */
+    float *group_reference = state + 3 * A2_QT;                /* [2][128] */
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q_block = blockIdx.x, head = blockIdx.y;
+    const uint32_t n_steps = (args.seq + A2_KV - 1) / A2_KV;
+    const long long budget = args.wait_cycles;
+
+    if ((base & 1023u) != 0) {  /* swizzled tiles need 1024-byte alignment */
+        if (threadIdx.x == 0) atomicMax(args.status, int(H3B_STATUS_ATTN_TIMEOUT));
+        return;
+    }
+    if (threadIdx.x == 0) {
+        *stop = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < A2_STAGES; s++) { mbar_init(go + 8 * s, 5); mbar_init(stage_free + 8 * s, 1); }
+        for (int b = 0; b < A2_S_BUFFERS; b++) {
+            mbar_init(s_full + 8 * b, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(pv_tail + 8 * b, 1);
+            for (int q = 0; q < 4; q++) mbar_init(ref_bar + 32 * b + 8 * q, 1);
+        }
+        mbar_init(o_done, 1);
+        for (int q = 0; q < 4; q++) { mbar_init(sum_bar + 8 * q, 2); mbar_init(out_bar + 8 * q, 2); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
+    if (threadIdx.x < A2_QT) row_reference[threadIdx.x] = -INFINITY;
+    if (warp == 1) tmem_alloc(tmem_holder, AT_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_holder));
+
+    if (warp == 0) {
+        /* ------------------------------------------------ TMA producer */
+        if (lane == 0) {
+            auto load = [&](uint32_t smem, const CUtensorMap *map, uint32_t bar, uint32_t row) {
+                tma_load_3d(smem, map, bar, 0, int(head), int(row));
+                tma_load_3d(smem + A2_TILE_BYTES / 2, map, bar, 64, int(head), int(row));
+            };
+            const uint32_t first = n_steps < 3 ? n_steps : 3;
+            mbar_expect_tx(q_full, (1 + first) * A2_TILE_BYTES);
+            load(q_smem, &map_q, q_full, q_block * A2_QT);
+            for (uint32_t j = 0; j < first; j++) load(k_smem + j * A2_TILE_BYTES, &map_k, q_full, j * A2_KV);
+            for (uint32_t j = 0; j < n_steps; j++) {
+                /* the stage is free once S(j) has been seen: Q.K(j)^T and P(j-3).V(j-3) are done */
+                const uint32_t stage = j % A2_STAGES;
+                if (!mbar_wait(stage_free + 8 * stage, (j / A2_STAGES) & 1u, stop, budget)) break;
+                const bool ahead = j + 3 < n_steps;
+                mbar_expect_tx(go + 8 * stage, (ahead ? 2 : 1) * A2_TILE_BYTES);
+                if (ahead) load(k_smem + stage * A2_TILE_BYTES, &map_k, go + 8 * stage, (j + 3) * A2_KV);
+                load(v_smem + stage * A2_TILE_BYTES, &map_v, go + 8 * stage, j * A2_KV);
+            }
+        }
+    } else if (warp == 1) {
+        /* -------------------------------------------------- MMA issuer */
+        /* The issuing warp is the scarcest resource of this kernel: the tensor pipe accepts the
+         * next MMA only when the one before has started (an M128 N128 K16 instruction occupies it
+         * for 72 cycles, measured), so every cycle this warp spends on anything else is a cycle
+         * the pipe idles. Hence: (a) the loop is unrolled by six (two barrier phases x three
+         * buffers), which makes every barrier address, phase and descriptor offset a constant;
+         * (b) the three barriers of step j+1 are tested (non-blocking) between the MMAs of step j,
+         * where the test's latency hides behind the pipe; only a failed test leads to a wait. */
+        const uint32_t leader = lane == 0;
+        constexpr uint32_t idesc_qk = instruction_desc(A2_QT, A2_KV);
+        constexpr uint32_t idesc_pv = instruction_desc(A2_QT, A2_D) | (1u << 16); /* B N-major */
+        constexpr uint32_t HALF = (A2_TILE_BYTES / 2) >> 4, STAGE = A2_TILE_BYTES >> 4;
+        const uint32_t q_lo0 = desc_lo_kmajor(q_smem);
+        const uint32_t k_lo0 = desc_lo_kmajor(k_smem);
+        const uint32_t v_lo0 = desc_lo_nmajor(v_smem, A2_TILE_BYTES / 2);
+        const uint32_t tmem_s0 = tmem_base + A2_COL_S, tmem_o = tmem_base + A2_COL_O;
+        /* scores of a step into S[buffer] from K stage `stage` (both step % 3) */
+        auto issue_qk = [&](uint32_t buffer) {
+            const uint32_t d = tmem_s0 + buffer * A2_KV;
+            const uint32_t k_lo = k_lo0 + buffer * STAGE;
+            umma_ss<false>(d, q_lo0, k_lo, idesc_qk, leader);
+#pragma unroll
+            for (int kk = 1; kk < A2_D / 16; kk++)
+                umma_ss<true>(d, q_lo0 + (kk >> 2) * HALF + 2 * (kk & 3), k_lo + (kk >> 2) * HALF + 2 * (kk & 3),
+                              idesc_qk, leader);
+            umma_commit_if(s_full + 8 * buffer, leader);
+        };
+        bool alive = __all_sync(0xffffffffu, mbar_wait(q_full, 0, stop, budget));
+        if (alive) {
+            tc_fence_after();
+            for (uint32_t j = 0; j < 3 && j < n_steps; j++) issue_qk(j);
+        }
+        /* has the barrier of the coming step been seen complete? */
+        uint32_t ready = 0;
+        /* one step; R = j mod 6 */
+        auto step = [&](auto r_const, uint32_t j) -> bool {
+            constexpr uint32_t R = decltype(r_const)::value;
+            constexpr uint32_t buffer = R % 3, round = (R / 3) & 1u;   /* S/P buffer and ring stage of step j */
+            constexpr uint32_t n_buffer = (R + 1) % 3, n_round = ((R + 1) / 3) & 1u;  /* of step j + 1 */
+            const bool ahead = j + 3 < n_steps;
+            if (!__all_sync(0xffffffffu, ready != 0u) &&
+                !__all_sync(0xffffffffu, mbar_wait(go + 8 * buffer, round, stop, budget)))
+                return false;
+            tc_fence_after();
+            const uint32_t v_lo = v_lo0 + buffer * STAGE;
+            const uint32_t a = tmem_s0 + buffer * A2_KV;
+            /* O += P(j).V(j): 8 P columns and 2048 bytes of V per 16 keys */
+            if (j == 0) umma_ts<false>(tmem_o, a, v_lo, idesc_pv, leader);
+            else umma_ts<true>(tmem_o, a, v_lo, idesc_pv, leader);
+#pragma unroll
+            for (uint32_t kk = 1; kk < 8; kk++) umma_ts<true>(tmem_o, a + kk * 8, v_lo + kk * (2048 >> 4), idesc_pv, leader);
+            /* a raise of the reference at step j + 1 waits for this product; from here on no later
+             * scores imply it */
+            if (j + 3 >= n_steps && j + 1 < n_steps) umma_commit_if(pv_tail + 8 * (j & 1u), leader);
+            /* S(j+3) = Q.K(j+3)^T into the buffer P(j) has just been read from (in-order pipe) */
+            const uint32_t d = tmem_s0 + buffer * A2_KV;
+            const uint32_t k_lo = k_lo0 + buffer * STAGE;
+            if (ahead) {
+                umma_ss<false>(d, q_lo0, k_lo, idesc_qk, leader);
+#pragma unroll
+                for (int kk = 1; kk < 6; kk++)
+                    umma_ss<true>(d, q_lo0 + (kk >> 2) * HALF + 2 * (kk & 3), k_lo + (kk >> 2) * HALF + 2 * (kk & 3),
+                                  idesc_qk, leader);
+            }
+            /* the barrier of step j + 1, tested while the pipe still has MMAs to run */
+            ready = mbar_test(go + 8 * n_buffer, n_round);
+            if (ahead) {
+#pragma unroll
+                for (int kk = 6; kk < 8; kk++)
+                    umma_ss<true>(d, q_lo0 + (kk >> 2) * HALF + 2 * (kk & 3), k_lo + (kk >> 2) * HALF + 2 * (kk & 3),
+                                  idesc_qk, leader);
+                umma_commit_if(s_full + 8 * buffer, leader);
+            }
+            return true;
+        };
+        for (uint32_t j = 0; alive && j < n_steps; j += 6) {
+            alive = step(std::integral_constant<uint32_t, 0>{}, j);
+            if (alive && j + 1 < n_steps) alive = step(std::integral_constant<uint32_t, 1>{}, j + 1);
+            if (alive && j + 2 < n_steps) alive = step(std::integral_constant<uint32_t, 2>{}, j + 2);
+            if (alive && j + 3 < n_steps) alive = step(std::integral_constant<uint32_t, 3>{}, j + 3);
+            if (alive && j + 4 < n_steps) alive = step(std::integral_constant<uint32_t, 4>{}, j + 4);
+            if (alive && j + 5 < n_steps) alive = step(std::integral_constant<uint32_t, 5>{}, j + 5);
+        }
+        if (alive) umma_commit_if(o_done, leader);
+    } else {
+        /* ------------------------------------------------------ softmax */
+        const uint32_t group = uint32_t(warp - 2) >> 2, quarter = warp & 3;
+        const uint32_t local_row = quarter * 32 + lane;
+        const uint32_t lane_base = (quarter * 32) << 16;
+        const uint32_t tmem_o = tmem_base + A2_COL_O + lane_base;
+        const uint32_t my_ref_bar = ref_bar + 32 * group + 8 * quarter;            /* I signal   */
+        const uint32_t their_ref_bar = ref_bar + 32 * (group ^ 1u) + 8 * quarter;  /* I wait for */
+        const float scale_log2 = args.scale_log2;
+        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+
+        float reference = -INFINITY;     /* the maximum my partial sum is relative to */
+        float sum = 0.0f;
+        bool alive = true;
+        for (uint32_t j = group; alive && j < n_steps; j += 2) {
+            const uint32_t buffer = j % A2_S_BUFFERS, round = (j / A2_S_BUFFERS) & 1u;
+            const uint32_t tmem_s = tmem_base + A2_COL_S + buffer * A2_KV + lane_base;   /* also P */
+            alive = __all_sync(0xffffffffu, mbar_wait(s_full + 8 * buffer, round, stop, budget));
+            if (!alive) break;
+            tc_fence_after();
+            /* S(j) is there, so Q.K(j)^T has finished and, being issued before it, so has
+             * P(j-3).V(j-3): the ring stage that held K(j) and V(j-3) is free; one thread says so */
+            if (quarter == 0 && lane == 0) mbar_arrive(stage_free + 8 * buffer);
+            /* asked early, needed after the maximum: has the other group decided step j - 1? */
+            bool ref_ready = j == 0 || mbar_try(their_ref_bar, ((j - 1) >> 1) & 1u);
+            uint32_t s[128];
+            tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            tmem_ld32(tmem_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+            tmem_ld32(tmem_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+            tmem_ld_wait();
+            const uint32_t valid = args.seq - j * A2_KV;
+            if (valid < uint32_t(A2_KV)) {
+#pragma unroll
+                for (int i = 0; i < 128; i++)
+                    if (uint32_t(i) >= valid) s[i] = 0xff800000u;        /* -inf */
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i += 8) {
+                mx0 = max3_f32(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                mx1 = max3_f32(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                mx2 = max3_f32(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                mx3 = max3_f32(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+            }
+            const float m_step = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+            /* the row's reference as the other group left it after step j - 1 */
+            if (!__all_sync(0xffffffffu, ref_ready)) {
+                alive = __all_sync(0xffffffffu, mbar_wait(their_ref_bar, ((j - 1) >> 1) & 1u, stop, budget));
+                if (!alive) break;
+            }
+            float row_ref = row_reference[local_row];
+            const bool raise = m_step - row_ref > AT_RESCALE_THRESHOLD;   /* also true at step 0 */
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                /* O must be at rest: P(j-1).V(j-1) complete, P(j) not published yet. Q.K(j+2)^T is
+                 * issued behind P(j-1).V(j-1), so the scores of step j+2 imply it; the last two
+                 * steps have barriers of their own */
+                alive = __all_sync(0xffffffffu,
+                                   j + 2 < n_steps
+                                       ? mbar_wait(s_full + 8 * ((j + 2) % A2_S_BUFFERS), ((j + 2) / A2_S_BUFFERS) & 1u,
+                                                   stop, budget)
+                                       : mbar_wait(pv_tail + 8 * ((j - 1) & 1u), 0, stop, budget));
+                if (!alive) break;
+                tc_fence_after();
+                const float alpha = raise ? fast_exp2(row_ref - m_step) : 1.0f;
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + c * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tmem_o + c * 32, o);
+                }
+                tmem_st_wait_all();
+                tc_fence_before();
+            }
+            if (raise) {
+                row_ref = m_step;
+                row_reference[local_row] = m_step;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(my_ref_bar);          /* release: the other group may decide */
+            /* my partial sum follows the reference */
+            if (reference != row_ref) {
+                sum *= reference == -INFINITY ? 0.0f : fast_exp2(reference - row_ref);
+                reference = row_ref;
+            }
+            const float neg_m = -row_ref;
+            const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
+            uint64_t sum_a = 0, sum_b = 0;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; chunk++) {                /* 32 keys -> 16 P columns */
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int e = 32 * chunk + 4 * i;
+                    const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])),
+                                                  scale2, neg_m2);
+                    const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])),
+                                                  scale2, neg_m2);
+                    float x0, x1, x2, x3;
+                    unpack_f32x2(xa, x0, x1);
+                    unpack_f32x2(xb, x2, x3);
+                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                    const float p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+                    sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
+                    sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
+                    packed[2 * i] = pack_bf16(p0, p1);
+                    packed[2 * i + 1] = pack_bf16(p2, p3);
+                }
+                tmem_st16(tmem_s + chunk * 16, packed);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(go + 8 * buffer);
+            float s0, s1, s2, s3;
+            unpack_f32x2(sum_a, s0, s1);
+            unpack_f32x2(sum_b, s2, s3);
+            sum += (s0 + s1) + (s2 + s3);
+        }
+        /* Combine the two groups' partial sums; normalise and store. Every MMA has completed once
+         * o_done fires, so the Q tile's shared memory is free for staging the output rows. */
+        group_sum[group * A2_QT + local_row] = sum;
+        group_reference[group * A2_QT + local_row] = reference;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sum_bar + 8 * quarter);
+        bool finished = alive && mbar_wait(sum_bar + 8 * quarter, 0, stop, budget) &&
+                        mbar_wait(o_done, 0, stop, budget);
+        finished = __all_sync(0xffffffffu, finished);
+        const uint32_t stage = q_smem + quarter * 8192;
+        if (finished) {
+            tc_fence_after();
+            const float ra = group_reference[local_row], rb = group_reference[A2_QT + local_row];
+            const float r = fmaxf(ra, rb);
+            float total = 0.0f;
+            if (ra != -INFINITY) total += group_sum[local_row] * fast_exp2(ra - r);
+            if (rb != -INFINITY) total += group_sum[A2_QT + local_row] * fast_exp2(rb - r);
+            const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+            /* group g owns output dims [64 g, 64 g + 64) of its rows */
+#pragma unroll 1
+            for (uint32_t c = 0; c < 2; c++) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + group * 64 + c * 32, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (uint32_t v = 0; v < 4; v++) {
+                    const uint32_t chunk = group * 8 + c * 4 + v;
+                    const uint32_t addr = stage + lane * 256 + ((chunk ^ (lane & 15)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv)),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv)),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv)),
+                                 "r"(pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv))
+                                 : "memory");
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(out_bar + 8 * quarter);
+            finished = __all_sync(0xffffffffu, mbar_wait(out_bar + 8 * quarter, 0, stop, budget));
+        }
+        if (finished) {
+            const uint32_t row0 = q_block * A2_QT + quarter * 32;
+            const uint32_t chunk = lane & 15;
+#pragma unroll 1
+            for (uint32_t i = 0; i < 8; i++) {
+                const uint32_t r = group * 16 + 2 * i + (lane >> 4);
+                const uint32_t out_row = row0 + r;
+                uint4 val;
+                const uint32_t addr = stage + r * 256 + ((chunk ^ (r & 15)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr) : "memory");
+                if (out_row < args.seq) {
+                    uint16_t *dst;
+                    if (PUSH) {
+                        const uint32_t owner = min(out_row / args.rows_local, args.world - 1);
+                        uint16_t *peer = args.peer_o[0];
+#pragma unroll
+                        for (uint32_t p = 1; p < 8; p++)
+                            if (p == owner) peer = args.peer_o[p];
+                        dst = peer + (size_t(out_row - owner * args.rows_local) * args.heads_total +
+                                      args.head0 + head) * A2_D;
+                    } else {
+                        dst = args.head_major ? args.out + (size_t(head) * args.seq + out_row) * A2_D
+                                              : args.out + (size_t(out_row) * args.heads + head) * A2_D;
+                    }
+                    *reinterpret_cast<uint4 *>(dst + chunk * 8) = val;
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*stop) {
+        if (threadIdx.x == 0) atomicMax(args.status, int(H3B_STATUS_ATTN_TIMEOUT));
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_free(tmem_base, AT_TMEM_COLS);
+    }
+}
+
 /* [rows][heads][128] BF16 viewed as a 3-D tensor (dim, head, row); box = 64 dims x 1 head x box_rows */
 bool make_qkv_map(CUtensorMap *map, const uint16_t *data, uint32_t rows, uint32_t heads,
                   uint32_t box_rows) {
@@ -799,6 +1226,9 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
                                  h3b_sdpa_tc<true, false>, h3b_sdpa_tc<true, true>})
                 ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 int(AT_SMEM)) == cudaSuccess;
+            for (auto *kernel : {h3b_sdpa_tc2<false>, h3b_sdpa_tc2<true>})
+                ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                int(A2_SMEM)) == cudaSuccess;
             if (!ok) {
                 cudaGetLastError();
                 return h3b_fail(gpu, "cannot reserve shared memory for the attention kernel");
@@ -806,8 +1236,12 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
             configured = true;
         }
         configure_guard.unlock();
+        /* dense calls take the kernel whose softmax groups alternate over key steps; the
+         * block-sparse mask (and H3B_SDPA_TWO_TILES=1) the one that alternates over two query tiles */
+        const char *pick = getenv("H3B_SDPA_TWO_TILES");
+        const bool step_kernel = !sparse && !(pick && *pick && strcmp(pick, "0") != 0);
         CUtensorMap map_q, map_k, map_v;
-        if (!make_qkv_map(&map_q, h3b_ptr<uint16_t>(query), seq, heads, AT_Q) ||
+        if (!make_qkv_map(&map_q, h3b_ptr<uint16_t>(query), seq, heads, step_kernel ? A2_QT : AT_Q) ||
             !make_qkv_map(&map_k, h3b_ptr<uint16_t>(key), seq, heads, AT_KV) ||
             !make_qkv_map(&map_v, h3b_ptr<uint16_t>(value), seq, heads, AT_KV))
             return h3b_fail(gpu, "cannot encode the attention tensor maps");
@@ -831,6 +1265,12 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         args.heads = heads;
         args.scale_log2 = scale * 1.4426950408889634f;
         args.head_major = head_major;
+        if (step_kernel) {
+            dim3 grid((seq + A2_QT - 1) / A2_QT, heads);
+            auto *kernel = peers ? h3b_sdpa_tc2<true> : h3b_sdpa_tc2<false>;
+            kernel<<<grid, A2_THREADS, A2_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
+            return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
+        }
         dim3 grid((seq + AT_Q - 1) / AT_Q, heads);
         auto *kernel = peers ? (sparse ? h3b_sdpa_tc<true, true> : h3b_sdpa_tc<true, false>)
                              : (sparse ? h3b_sdpa_tc<false, true> : h3b_sdpa_tc<false, false>);

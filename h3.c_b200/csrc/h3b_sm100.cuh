@@ -42,6 +42,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
+/* Non-blocking look at a phase (try_wait may suspend the thread for a while when the phase is
+ * still open; this returns at once). 1 when the phase with this parity has completed. */
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+
 /* Bounded wait: gives up after `limit` cycles of the SM clock without progress (the context's
  * wait budget, about a second by default). Returns false when the CTA should stop. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *stop,

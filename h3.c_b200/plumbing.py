@@ -81,3 +81,26 @@ class NcclPair:
                d.P2POp(d.irecv, self.memory.torch_of(out), self.partner)]
         for req in d.batch_isend_irecv(ops):
             req.wait()
+
+
+def load_bf16_once(dist, memory, gpu, path, file_offset, elements, rank, source=0):
+    """Checkpoint tensor for every rank of the node with one pass over the file: the source rank
+    reads it from disk into its tensor (the library's chunked, multi-threaded loader), then NCCL
+    broadcasts it over NVLink; with N ranks the file system serves 1/N of what N independent
+    loads would ask of it (38.5 GB of block weights per rank for the full model). Returns this
+    rank's tensor (torch allocation wrapped into a library tensor)."""
+    import ctypes as C
+    tensor = memory.bf16(elements)
+    problem = None
+    if rank == source:
+        error = C.create_string_buffer(400)
+        if not gpu.lib.h3_gpu_tensor_read_file_bf16(tensor.handle, str(path).encode(), file_offset, elements,
+                                                    error, len(error)):
+            problem = error.value.decode() or "tensor file read failed"
+    # every rank learns whether the read worked before anybody enters the collective on garbage
+    outcome = [problem]
+    dist.broadcast_object_list(outcome, src=source)
+    if outcome[0]:
+        raise RuntimeError(f"load_bf16_once: {outcome[0]}")
+    dist.broadcast(memory.torch_of(tensor), src=source)
+    return tensor

@@ -316,7 +316,15 @@ def test_qkv_rope(gpu, pkg, seq, heads, hd, half, grouped):
     (64, 1, 128), (65, 2, 128), (128, 1, 128), (129, 3, 128), (1000, 4, 128), (1, 1, 128),
 ])
 @pytest.mark.parametrize("head_major", [0, 1])
-def test_sdpa(gpu, pkg, seq, heads, hd, head_major):
+@pytest.mark.parametrize("two_tiles", [False, True])
+def test_sdpa(gpu, pkg, monkeypatch, seq, heads, hd, head_major, two_tiles):
+    """Dense attention on both tensor-core kernels: the default (one query tile per CTA, softmax
+    groups alternating over key steps) and the one the block-sparse mask uses (two query tiles in
+    ping-pong), which H3B_SDPA_TWO_TILES=1 selects for dense calls too."""
+    if two_tiles:
+        if hd != 128:
+            pytest.skip("head_dim != 128 takes the SIMT kernel either way")
+        monkeypatch.setenv("H3B_SDPA_TWO_TILES", "1")
     n = seq * heads * hd
     scale = 1.0 / np.sqrt(hd)
     name = "sdpa_bf16_head_major_output" if head_major else "sdpa_bf16"
@@ -337,9 +345,12 @@ def test_sdpa(gpu, pkg, seq, heads, hd, head_major):
     assert_aggregate_close(to.read(), want, f"sdpa normal {seq}x{heads}x{hd}", rel_l2=4e-3, max_abs=2e-2)
 
 
-def test_sdpa_sharp_scores_rescale(gpu, pkg):
+@pytest.mark.parametrize("two_tiles", [False, True])
+def test_sdpa_sharp_scores_rescale(gpu, pkg, monkeypatch, two_tiles):
     """Scores whose running maximum keeps growing by more than the lazy-rescale threshold:
     keys are scaled up along the sequence so every tile raises the maximum."""
+    if two_tiles:
+        monkeypatch.setenv("H3B_SDPA_TWO_TILES", "1")
     seq, heads, hd = 700, 2, 128
     n = seq * heads * hd
     q = o.from_bf16(bf(n, 1)).reshape(seq, heads, hd)

@@ -31,9 +31,10 @@ def checkpoint(tmp_path_factory):
     return directory
 
 
-def run_host(which, checkpoint, out, layout, steps, core_reuse, token_reduction, passes, extra_env=None):
+def run_host(which, checkpoint, out, layout, steps, core_reuse, token_reduction, passes, extra_env=None,
+             ssd_streaming=0):
     cmd = [str(HOSTS[which]), str(checkpoint), str(out), *map(str, layout), str(steps), str(core_reuse),
-           str(token_reduction), "0", *passes]
+           str(token_reduction), str(ssd_streaming), *passes]
     env = dict(os.environ, **(extra_env or {}))
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
     print(which, res.stdout.strip().replace("\n", "\n" + which + " "))
@@ -115,3 +116,17 @@ def test_reference_host_speed_modes_on_both_backends(checkpoint, tmp_path):
                      extra_env={"H3_CUDA_SDPA_FA2": "0"})
     check_against_floor(["forward velocity", "final latents, token reduction + core reuse"], out["b200"], floor,
                         out["reference"])
+
+
+@needs_hosts
+def test_reference_host_weight_streaming_gives_the_resident_result(checkpoint, tmp_path):
+    """The reference's SSD-streaming mode (h3_dit.c:2355-2433): block weights are not resident,
+    an I/O thread fills one of two slots through h3_gpu_tensor_stream_file_bf16 while the other
+    slot's block runs. Same kernels, same weights: on this backend the result must equal the
+    resident run bit for bit, which it only does if the streamed bytes are in place before the
+    block that uses them starts and are not overwritten while it runs."""
+    layout, passes = (32, 3, 16, 16, 11), ["euler:1"]
+    resident = run_host("b200", checkpoint, tmp_path / "resident.bin", layout, 2, 1, 0, passes)
+    streamed = run_host("b200", checkpoint, tmp_path / "streamed.bin", layout, 2, 1, 0, passes, ssd_streaming=1)
+    for (rv, ra), (sv, sa) in zip(resident, streamed):
+        assert np.array_equal(rv, sv) and np.array_equal(ra, sa)

@@ -90,18 +90,26 @@ def test_registration_validation(pkg):
 
 
 @pytest.mark.parametrize("seq", [512, 700])
-def test_full_mask_is_dense(pkg, seq):
+def test_full_mask_is_dense(pkg, seq, monkeypatch):
+    """A mask that lists every key tile gives bit for bit what the same kernel gives without a
+    mask (H3B_SDPA_TWO_TILES=1 makes dense calls take the kernel that walks masks), and the
+    default dense kernel agrees with it to the rounding of the probabilities."""
     heads = 2
     q, k, v = qkv(seq, heads, 1)
     qb, kt = (seq + 127) // 128, (seq + 63) // 64
     gpu = pkg.Gpu(0)
     try:
+        default_dense = run_sdpa(pkg, gpu, q, k, v, seq, heads)
+        monkeypatch.setenv("H3B_SDPA_TWO_TILES", "1")
         dense = run_sdpa(pkg, gpu, q, k, v, seq, heads)
+        monkeypatch.delenv("H3B_SDPA_TWO_TILES")
         assert set_sparse(gpu, *csr([np.arange(kt)] * qb), seq) == 1
         masked = run_sdpa(pkg, gpu, q, k, v, seq, heads)
     finally:
         gpu.close()
     assert np.array_equal(dense, masked)
+    a, b = o.from_bf16(default_dense), o.from_bf16(dense)
+    assert np.linalg.norm(a - b) <= 4e-3 * np.linalg.norm(b)
 
 
 @pytest.mark.parametrize("seq,kind", [(512, "random"), (700, "random"), (1100, "window"), (700, "halves")])

@@ -71,3 +71,28 @@ def test_guidance_groups_match_oracle(world):
     print(res.stdout[-2000:])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert "PASS" in res.stdout
+
+
+def test_checkpoint_tensor_is_read_once_and_broadcast(tmp_path):
+    """One rank reads a checkpoint tensor from disk, NCCL hands it to the others over NVLink
+    (h3.c_b200/plumbing.py load_bf16_once): with N ranks the file is read once, not N times."""
+    import numpy as np
+    n = gpu_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2
+    rng = np.random.default_rng(5)
+    elements = (40 << 20) // 2 + 77
+    path = tmp_path / "weights.bin"
+    with open(path, "wb") as f:
+        f.write(b"x" * 100)
+        f.write(rng.integers(0, 1 << 16, elements, dtype=np.uint16).tobytes())
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    port = 29200 + os.getpid() % 300
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                          f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
+                          str(ROOT / "tests" / "broadcast_worker.py"), str(path), "100", str(elements)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    print(res.stdout[-1500:])
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-3000:]
+    assert "PASS" in res.stdout
