@@ -765,7 +765,7 @@ def run_gpu_arm(args, shape, sequence, text_rows):
         if "attention" in kernels:
             at_ms, at_tf = kernels["attention"]
             roofline["furthest_from_roof"] = {
-                "kernel": "h3b_sdpa_tc (joint attention)", "achieved": at_tf,
+                "kernel": "h3b_sdpa_tc2 (joint attention)", "achieved": at_tf,
                 "frac": at_tf / peaks["bf16_tflops"], "ms_per_launch": at_ms}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
