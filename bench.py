@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -934,6 +935,24 @@ def run_cfg_arm(args, shape, sequence, text_rows):
     gpu.close()
 
 
+def run_sdpa_only(pkg, rows, heads):
+    """Three launches of the dense attention kernel on its own: a case small enough for a
+    multi-section profiler capture (rows x heads x 128 x 3 inputs; 6400,12 holds 118 MB)."""
+    import torch
+    gpu = pkg.Gpu(0)
+    count = rows * heads * 128
+    generator = torch.Generator(device="cuda").manual_seed(1)
+    tensors = [torch.randn(count, device="cuda", dtype=torch.bfloat16, generator=generator) for _ in range(3)]
+    tensors.append(torch.empty(count, device="cuda", dtype=torch.bfloat16))
+    q, k, v, out = [gpu.wrap(t.data_ptr(), count, pkg.BF16) for t in tensors]
+    for _ in range(3):
+        gpu.begin()
+        gpu.op("sdpa_bf16", out, q, k, v, rows, heads, 128, 1.0 / math.sqrt(128))
+        gpu.submit()
+    print(f"sdpa {rows} x {heads} x 128: mean |out| = {float(tensors[3].float().abs().mean()):.4f}")
+    gpu.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -951,6 +970,9 @@ def main():
                     help="N>1: peer stores fused into the kernels, or pack + NCCL all-to-all + unpack; "
                          "loopback = same kernels with the stores kept local and no barriers, to "
                          "measure the exposed cost of the exchange (results invalid)")
+    ap.add_argument("--sdpa-only", metavar="ROWS,HEADS", default=None,
+                    help="profiler target: three dense attention launches (head_dim 128, N(0,1) inputs) "
+                         "and nothing else; prints no bench line")
     ap.add_argument("--euler-steps", type=int, default=20, help="c5: Euler steps per denoise")
     ap.add_argument("--guidance", type=float, default=5.0,
                     help="c5: guidance scale (the reference has no guidance pass; harness parameter)")
@@ -959,6 +981,9 @@ def main():
 
     import __graft_entry__ as entry
     pkg = entry.load_package()
+    if args.sdpa_only:
+        run_sdpa_only(pkg, *map(int, args.sdpa_only.split(",")))
+        return
     text_rows, video_rows, _ = WORKLOADS[args.workload]
     shape = pkg.DitShape(blocks=args.blocks)
     sequence = text_rows + video_rows
