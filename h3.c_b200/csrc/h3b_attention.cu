@@ -192,8 +192,15 @@ h3b_qkv_rope_generic(const uint16_t *qkv, const uint16_t *q_norm, const uint16_t
 constexpr int kSimtThreads = 128;
 constexpr int kSimtMaxDimsPerThread = 4; /* head_dim <= 512 */
 
+__device__ __forceinline__ float simt_load(const uint16_t *p) { return h3b_widen(*p); }
+__device__ __forceinline__ float simt_load(const float *p) { return *p; }
+__device__ __forceinline__ void simt_store(uint16_t *p, float v) { *p = h3b_narrow(v); }
+__device__ __forceinline__ void simt_store(float *p, float v) { *p = v; }
+
+/* T = uint16_t (BF16) or float: the arithmetic is F32 either way */
+template <typename T>
 __global__ void __launch_bounds__(kSimtThreads)
-h3b_sdpa_simt(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out,
+h3b_sdpa_simt(const T *q, const T *k, const T *v, T *out,
               uint32_t seq, uint32_t heads, uint32_t hd, float scale, int head_major) {
     extern __shared__ float simt_smem[];
     float *qs = simt_smem;              /* hd          */
@@ -202,8 +209,8 @@ h3b_sdpa_simt(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t 
     __shared__ float bcast;
     const uint32_t row = blockIdx.x, head = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint16_t *qp = q + (size_t(row) * heads + head) * hd;
-    for (uint32_t d = tid; d < hd; d += kSimtThreads) qs[d] = h3b_widen(qp[d]);
+    const T *qp = q + (size_t(row) * heads + head) * hd;
+    for (uint32_t d = tid; d < hd; d += kSimtThreads) qs[d] = simt_load(qp + d);
     __syncthreads();
     float m = -INFINITY, l = 0.0f;
     float acc[kSimtMaxDimsPerThread] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -211,9 +218,9 @@ h3b_sdpa_simt(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t 
         const uint32_t j = j0 + tid;
         float s = -INFINITY;
         if (j < seq) {
-            const uint16_t *kp = k + (size_t(j) * heads + head) * hd;
+            const T *kp = k + (size_t(j) * heads + head) * hd;
             float dot = 0.0f;
-            for (uint32_t d = 0; d < hd; d++) dot = fmaf(qs[d], h3b_widen(kp[d]), dot);
+            for (uint32_t d = 0; d < hd; d++) dot = fmaf(qs[d], simt_load(kp + d), dot);
             s = dot * scale;
         }
         float tile_max = s;
@@ -246,7 +253,7 @@ h3b_sdpa_simt(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t 
             if (d >= hd) break;
             float a = acc[i] * alpha;
             for (uint32_t t = 0; t < live; t++)
-                a = fmaf(ps[t], h3b_widen(v[(size_t(j0 + t) * heads + head) * hd + d]), a);
+                a = fmaf(ps[t], simt_load(v + (size_t(j0 + t) * heads + head) * hd + d), a);
             acc[i] = a;
         }
         __syncthreads();
@@ -258,7 +265,7 @@ h3b_sdpa_simt(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t 
         if (d >= hd) break;
         const size_t o = head_major ? (size_t(head) * seq + row) * hd + d
                                     : (size_t(row) * heads + head) * hd + d;
-        out[o] = h3b_narrow(acc[i] * inv);
+        simt_store(out + o, acc[i] * inv);
     }
 }
 
@@ -1281,7 +1288,7 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         return h3b_fail(gpu, "SDPA head dimension is too large");
     dim3 grid(seq, heads);
     size_t smem = (size_t(hd) + kSimtThreads) * sizeof(float);
-    h3b_sdpa_simt<<<grid, kSimtThreads, smem, gpu->stream>>>(
+    h3b_sdpa_simt<uint16_t><<<grid, kSimtThreads, smem, gpu->stream>>>(
         h3b_ptr<uint16_t>(query), h3b_ptr<uint16_t>(key), h3b_ptr<uint16_t>(value),
         h3b_ptr<uint16_t>(output), seq, heads, hd, scale, head_major);
     return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
@@ -1418,6 +1425,58 @@ extern "C" int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *ou
                                                   uint32_t heads, uint32_t head_dim,
                                                   float scale) {
     return sdpa_common(gpu, output, query, key, value, sequence, heads, head_dim, scale, 1);
+}
+
+/* F32 attention (the video-VAE decoder's, head_dim 64). Like the reference (h3_cuda_attention.cu:
+ * 2990-3013) head sizes 64 and 128 go through the BF16 tensor-core kernel: q, k and v are rounded
+ * to BF16 into scratch and the result is widened again; head_dim 64 is padded with zeros to the
+ * kernel's 128 (zero dims add nothing to a score, and the output's extra dims are dropped).
+ * Other head sizes, and H3B_SDPA_F32_EXACT=1 (the reference's H3_CUDA_SDPA_F32_EXACT), take the
+ * F32 SIMT kernel. */
+extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                               const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                               uint32_t sequence, uint32_t heads, uint32_t head_dim, float scale) {
+    const size_t count = size_t(sequence) * heads * head_dim;
+    if (!sequence || !heads || !head_dim) return h3b_fail(gpu, "SDPA shape is empty");
+    if (!h3b_need(gpu, query, H3_GPU_F32, count, "SDPA query") ||
+        !h3b_need(gpu, key, H3_GPU_F32, count, "SDPA key") ||
+        !h3b_need(gpu, value, H3_GPU_F32, count, "SDPA value") ||
+        !h3b_need(gpu, output, H3_GPU_F32, count, "SDPA output") || !h3b_need_command(gpu))
+        return 0;
+    const char *exact = getenv("H3B_SDPA_F32_EXACT");
+    const bool aligned = h3b_aligned16(query->data) && h3b_aligned16(key->data) &&
+                         h3b_aligned16(value->data) && h3b_aligned16(output->data);
+    if ((head_dim == 64 || head_dim == 128) && aligned && scale > 0.0f && h3b_tensor_map_available() &&
+        !(exact && *exact && strcmp(exact, "0") != 0) && !getenv("H3B_SDPA_SIMT")) {
+        const size_t units = size_t(sequence) * heads, padded = units * AT_D;
+        uint16_t *scratch = static_cast<uint16_t *>(h3b_workspace(gpu, 4 * padded * sizeof(uint16_t)));
+        if (!scratch) return h3b_fail(gpu, "sdpa_f32: cannot allocate the BF16 operands");
+        h3_gpu_tensor half[4];
+        for (int i = 0; i < 4; i++) {
+            half[i] = h3_gpu_tensor{scratch + i * padded, padded, padded * sizeof(uint16_t), H3_GPU_BF16, gpu, 1};
+        }
+        h3b_f32_to_bf16_pad(gpu, h3b_ptr<float>(query), scratch, units, head_dim, AT_D);
+        h3b_f32_to_bf16_pad(gpu, h3b_ptr<float>(key), scratch + padded, units, head_dim, AT_D);
+        h3b_f32_to_bf16_pad(gpu, h3b_ptr<float>(value), scratch + 2 * padded, units, head_dim, AT_D);
+        if (!h3b_launched(gpu, "sdpa_f32 operands")) return 0;
+        /* a block-sparse mask registered for the DiT's BF16 attention does not apply here (the
+         * reference passes none on this route, h3_cuda_attention.cu:3010) */
+        const uint32_t masked_rows = gpu->sparse_rows;
+        gpu->sparse_rows = 0;
+        const int ok = sdpa_common(gpu, &half[3], &half[0], &half[1], &half[2], sequence, heads, AT_D, scale, 0);
+        gpu->sparse_rows = masked_rows;
+        if (!ok) return 0;
+        h3b_bf16_to_f32_unpad(gpu, scratch + 3 * padded, h3b_ptr<float>(output), units, head_dim, AT_D);
+        return h3b_launched(gpu, "sdpa_f32 result");
+    }
+    if (head_dim > uint32_t(kSimtThreads * kSimtMaxDimsPerThread))
+        return h3b_fail(gpu, "SDPA head dimension is too large");
+    dim3 grid(sequence, heads);
+    const size_t smem = (size_t(head_dim) + kSimtThreads) * sizeof(float);
+    h3b_sdpa_simt<float><<<grid, kSimtThreads, smem, gpu->stream>>>(
+        h3b_ptr<float>(query), h3b_ptr<float>(key), h3b_ptr<float>(value), h3b_ptr<float>(output), sequence,
+        heads, head_dim, scale, 0);
+    return h3b_launched(gpu, "sdpa_f32", H3B_SDPA);
 }
 
 /* ---- sequence-parallel variants: the exchange is the kernels' own peer stores ---- */

@@ -187,6 +187,7 @@ enum h3b_gemm_epilogue {
     H3B_EPI_STORE = 0,    /* out[r][c] = bf16(acc + bias[c])                          */
     H3B_EPI_SWIGLU = 1,   /* W = [gate rows | up rows]; out[r][c] = swiglu, n = hidden */
     H3B_EPI_QKV_ROPE = 2, /* grouped QKV: per-head RMSNorm + RoPE, writes q/k/v directly   */
+    H3B_EPI_STORE_F32 = 3, /* out[r][c] = acc + bias[c], F32 output and bias                */
 };
 /* Fused QKV projection + per-head RMSNorm + RoPE for head_dim 128, rope_half 48, grouped
  * layout. Returns -1 when the shape cannot take the fused kernel (caller runs the two-step
@@ -206,3 +207,16 @@ int h3b_qkv_rope_launch(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, cons
                         const uint16_t *rs, uint32_t seq, uint32_t heads, uint32_t hd,
                         uint32_t rope_half, int grouped, float eps);
 bool h3b_tensor_map_available();
+/* F32 projection on the BF16 tensor cores: C[rows,n] = X[rows,k] . W[n,k]^T (+bias), all F32 in
+ * memory. X and W are split into BF16 pairs hi + lo and the three products hi.hi + hi.lo +
+ * lo.hi are summed in the F32 accumulator by one GEMM over 3k (products carry ~16 mantissa
+ * bits; the reference's route for the same call is TF32, 10 bits, h3_cuda_gemm.cu:242-254).
+ * Returns -1 when the shape cannot take it (caller runs the exact F32 kernel). */
+int h3b_gemm_f32_split(h3_gpu *gpu, float *out, const float *x, const float *w, const float *bias,
+                       uint32_t rows, uint32_t k, uint32_t n);
+/* conversion kernels (h3b_f32ops.cu) */
+void h3b_f32_to_bf16_pad(h3_gpu *gpu, const float *in, uint16_t *out, size_t units, uint32_t dims,
+                         uint32_t padded);
+void h3b_bf16_to_f32_unpad(h3_gpu *gpu, const uint16_t *in, float *out, size_t units, uint32_t dims,
+                           uint32_t padded);
+void h3b_split_bf16(h3_gpu *gpu, const float *in, uint16_t *out, size_t rows, uint32_t k, bool weight);

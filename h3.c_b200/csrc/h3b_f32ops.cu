@@ -1,0 +1,398 @@
+/* F32 row operations of the video-VAE decoder's transformer (the step after the DiT on the
+ * reference's pipeline): RMSNorm, LayerNorm, residual + branch * scale, SwiGLU, and the QKV
+ * split with unweighted per-head RMS norm and RoPE. They replace h3k_rms_norm_f32,
+ * h3k_layer_norm_f32, h3k_scale_add_f32, h3k_swiglu_f32 (h3_cuda_core.cu:57-66, 92-103,
+ * 161-182, 212-250) and h3k_video_qkv_rope_f32 (h3_cuda_attention.cu:125-170) behind the same
+ * entry points, with the reference's argument checks (h3_cuda_core.cu:609-628, 673-684,
+ * 720-772; h3_cuda_attention.cu:2657-2682).
+ *
+ * All of them are bandwidth-bound: 16-byte accesses where width and pointers allow, one CTA
+ * per row for the norms (the row is read from HBM once and again from L1 for the second and
+ * third pass), everything F32 like the reference (its tests hold these to 1e-5).
+ *
+ * The same file holds the small conversion kernels the F32 attention and F32 projection
+ * routes need (F32 -> BF16 with head padding, BF16 -> F32, F32 -> split BF16 triples).
+ */
+#include "h3b_common.cuh"
+
+#include <cmath>
+#include <initializer_list>
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+inline unsigned blocks_for(size_t count, unsigned threads) {
+    return unsigned((count + threads - 1) / threads);
+}
+
+inline bool aligned16(std::initializer_list<const void *> pointers) {
+    for (const void *p : pointers)
+        if (reinterpret_cast<uintptr_t>(p) & 15u) return false;
+    return true;
+}
+
+/* sum over the CTA; every thread gets the result */
+__device__ __forceinline__ float cta_sum(float value, float *scratch) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) value += __shfl_xor_sync(0xffffffffu, value, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();                       /* scratch may still be read from the previous call */
+    if (lane == 0) scratch[warp] = value;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; w++) total += scratch[w];
+    return total;
+}
+
+/* y = x * rsqrt(mean(x^2) + eps) * weight */
+template <bool VEC>
+__global__ void __launch_bounds__(kRowThreads)
+h3b_rms_norm_f32_kernel(const float *__restrict__ input, const float *__restrict__ weight,
+                        float *__restrict__ output, uint32_t width, float epsilon) {
+    __shared__ float scratch[kRowThreads / 32];
+    const float *x = input + size_t(blockIdx.x) * width;
+    float *y = output + size_t(blockIdx.x) * width;
+    float local = 0.0f;
+    if (VEC) {
+        for (uint32_t i = threadIdx.x; i < width / 4; i += kRowThreads) {
+            const float4 v = reinterpret_cast<const float4 *>(x)[i];
+            local = fmaf(v.x, v.x, local); local = fmaf(v.y, v.y, local);
+            local = fmaf(v.z, v.z, local); local = fmaf(v.w, v.w, local);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < width; i += kRowThreads) local = fmaf(x[i], x[i], local);
+    }
+    const float inverse = 1.0f / sqrtf(cta_sum(local, scratch) / float(width) + epsilon);
+    if (VEC) {
+        for (uint32_t i = threadIdx.x; i < width / 4; i += kRowThreads) {
+            const float4 v = reinterpret_cast<const float4 *>(x)[i];
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(weight) + i);
+            reinterpret_cast<float4 *>(y)[i] =
+                make_float4(v.x * inverse * w.x, v.y * inverse * w.y, v.z * inverse * w.z, v.w * inverse * w.w);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < width; i += kRowThreads) y[i] = x[i] * inverse * weight[i];
+    }
+}
+
+/* y = (x - mean) * rsqrt(var + eps) * weight + bias, variance of the centred values */
+template <bool VEC>
+__global__ void __launch_bounds__(kRowThreads)
+h3b_layer_norm_f32_kernel(const float *__restrict__ input, const float *__restrict__ weight,
+                          const float *__restrict__ bias, float *__restrict__ output, uint32_t width,
+                          float epsilon) {
+    __shared__ float scratch[kRowThreads / 32];
+    const float *x = input + size_t(blockIdx.x) * width;
+    float *y = output + size_t(blockIdx.x) * width;
+    float local = 0.0f;
+    if (VEC) {
+        for (uint32_t i = threadIdx.x; i < width / 4; i += kRowThreads) {
+            const float4 v = reinterpret_cast<const float4 *>(x)[i];
+            local += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < width; i += kRowThreads) local += x[i];
+    }
+    const float mean = cta_sum(local, scratch) / float(width);
+    local = 0.0f;
+    if (VEC) {
+        for (uint32_t i = threadIdx.x; i < width / 4; i += kRowThreads) {
+            const float4 v = reinterpret_cast<const float4 *>(x)[i];
+            const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+            local = fmaf(a, a, local); local = fmaf(b, b, local);
+            local = fmaf(c, c, local); local = fmaf(d, d, local);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < width; i += kRowThreads) {
+            const float a = x[i] - mean;
+            local = fmaf(a, a, local);
+        }
+    }
+    const float inverse = 1.0f / sqrtf(cta_sum(local, scratch) / float(width) + epsilon);
+    if (VEC) {
+        for (uint32_t i = threadIdx.x; i < width / 4; i += kRowThreads) {
+            const float4 v = reinterpret_cast<const float4 *>(x)[i];
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(weight) + i);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(bias) + i);
+            reinterpret_cast<float4 *>(y)[i] =
+                make_float4((v.x - mean) * inverse * w.x + b.x, (v.y - mean) * inverse * w.y + b.y,
+                            (v.z - mean) * inverse * w.z + b.z, (v.w - mean) * inverse * w.w + b.w);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < width; i += kRowThreads)
+            y[i] = (x[i] - mean) * inverse * weight[i] + bias[i];
+    }
+}
+
+/* out = residual + branch * scale[column] */
+template <bool VEC>
+__global__ void h3b_scale_add_f32_kernel(const float *__restrict__ residual, const float *__restrict__ branch,
+                                         const float *__restrict__ scale, float *__restrict__ output,
+                                         size_t items, uint32_t width) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= items) return;
+    if (VEC) {
+        const uint32_t column = uint32_t((i * 4) % width);
+        const float4 r = reinterpret_cast<const float4 *>(residual)[i];
+        const float4 b = reinterpret_cast<const float4 *>(branch)[i];
+        const float4 s = __ldg(reinterpret_cast<const float4 *>(scale + column));
+        reinterpret_cast<float4 *>(output)[i] =
+            make_float4(r.x + b.x * s.x, r.y + b.y * s.y, r.z + b.z * s.z, r.w + b.w * s.w);
+    } else {
+        output[i] = residual[i] + branch[i] * scale[i % width];
+    }
+}
+
+__device__ __forceinline__ float silu_times(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
+
+/* fused rows are [gate (width) | up (width)]; out = silu(gate) * up */
+template <bool VEC>
+__global__ void h3b_swiglu_f32_kernel(const float *__restrict__ fused, float *__restrict__ output, size_t items,
+                                      uint32_t width) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= items) return;
+    if (VEC) {
+        const size_t row = (i * 4) / width;
+        const uint32_t column = uint32_t((i * 4) % width);
+        const float *base = fused + row * width * 2;
+        const float4 g = *reinterpret_cast<const float4 *>(base + column);
+        const float4 u = *reinterpret_cast<const float4 *>(base + width + column);
+        reinterpret_cast<float4 *>(output)[i] =
+            make_float4(silu_times(g.x, u.x), silu_times(g.y, u.y), silu_times(g.z, u.z), silu_times(g.w, u.w));
+    } else {
+        const size_t row = i / width;
+        const uint32_t column = uint32_t(i % width);
+        output[i] = silu_times(fused[row * width * 2 + column], fused[row * width * 2 + width + column]);
+    }
+}
+
+/* One warp per (row, head). Fused rows are [head][q | k | v][dim]; q and k get an unweighted RMS
+ * norm over the head, then RoPE on the first 2 * rope_half dims (pairs (d, d + rope_half)); v is
+ * copied. */
+__global__ void __launch_bounds__(256)
+h3b_video_qkv_rope_f32_kernel(const float *__restrict__ qkv, const float *__restrict__ rope_cos,
+                              const float *__restrict__ rope_sin, float *__restrict__ query,
+                              float *__restrict__ key, float *__restrict__ value, uint32_t sequence,
+                              uint32_t heads, uint32_t head_dim, uint32_t rope_half, float epsilon) {
+    const size_t unit = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    if (unit >= size_t(sequence) * heads) return;
+    const uint32_t row = uint32_t(unit / heads);
+    const float *q = qkv + unit * head_dim * 3, *k = q + head_dim, *v = k + head_dim;
+    float q_sum = 0.0f, k_sum = 0.0f;
+    for (uint32_t d = lane; d < head_dim; d += 32) {
+        q_sum = fmaf(q[d], q[d], q_sum);
+        k_sum = fmaf(k[d], k[d], k_sum);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        q_sum += __shfl_xor_sync(0xffffffffu, q_sum, o);
+        k_sum += __shfl_xor_sync(0xffffffffu, k_sum, o);
+    }
+    const float q_inverse = 1.0f / sqrtf(q_sum / float(head_dim) + epsilon);
+    const float k_inverse = 1.0f / sqrtf(k_sum / float(head_dim) + epsilon);
+    const float *cosine = rope_cos + size_t(row) * rope_half, *sine = rope_sin + size_t(row) * rope_half;
+    float *q_out = query + unit * head_dim, *k_out = key + unit * head_dim, *v_out = value + unit * head_dim;
+    for (uint32_t d = lane; d < head_dim; d += 32) {
+        float q0 = q[d] * q_inverse, k0 = k[d] * k_inverse;
+        if (d < rope_half) {
+            const float q1 = q[d + rope_half] * q_inverse, k1 = k[d + rope_half] * k_inverse;
+            const float c = cosine[d], s = sine[d];
+            q0 = q0 * c - q1 * s;
+            k0 = k0 * c - k1 * s;
+        } else if (d < rope_half * 2) {
+            const float q1 = q[d - rope_half] * q_inverse, k1 = k[d - rope_half] * k_inverse;
+            const float c = cosine[d - rope_half], s = sine[d - rope_half];
+            q0 = q0 * c + q1 * s;
+            k0 = k0 * c + k1 * s;
+        }
+        q_out[d] = q0;
+        k_out[d] = k0;
+        v_out[d] = v[d];
+    }
+}
+
+/* F32 [units][dims] -> BF16 [units][padded], zeros behind the dims (4 output values per thread) */
+__global__ void h3b_f32_to_bf16_pad_kernel(const float *__restrict__ in, uint16_t *__restrict__ out, size_t units,
+                                           uint32_t dims, uint32_t padded) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint32_t groups = padded / 4;
+    if (i >= units * groups) return;
+    const size_t unit = i / groups;
+    const uint32_t d = uint32_t(i % groups) * 4;
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (d < dims) v = *reinterpret_cast<const float4 *>(in + unit * dims + d);
+    *reinterpret_cast<uint2 *>(out + unit * padded + d) =
+        make_uint2(uint32_t(h3b_narrow(v.x)) | uint32_t(h3b_narrow(v.y)) << 16,
+                   uint32_t(h3b_narrow(v.z)) | uint32_t(h3b_narrow(v.w)) << 16);
+}
+
+/* BF16 [units][padded] -> F32 [units][dims] */
+__global__ void h3b_bf16_to_f32_unpad_kernel(const uint16_t *__restrict__ in, float *__restrict__ out, size_t units,
+                                             uint32_t dims, uint32_t padded) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint32_t groups = dims / 4;
+    if (i >= units * groups) return;
+    const size_t unit = i / groups;
+    const uint32_t d = uint32_t(i % groups) * 4;
+    const uint2 v = *reinterpret_cast<const uint2 *>(in + unit * padded + d);
+    *reinterpret_cast<float4 *>(out + unit * dims + d) =
+        make_float4(h3b_lo(v.x), h3b_hi(v.x), h3b_lo(v.y), h3b_hi(v.y));
+}
+
+/* F32 [rows][k] -> BF16 [rows][3k]: x = hi + lo with hi = bf16(x), lo = bf16(x - hi). The
+ * activation side writes [hi | hi | lo], the weight side [hi | lo | hi], so that the dot product of
+ * two such rows is hi.hi + hi.lo + lo.hi: every product of an F32 projection to ~2^-16, summed
+ * in the tensor core's F32 accumulator. */
+template <bool WEIGHT>
+__global__ void h3b_split_bf16_kernel(const float *__restrict__ in, uint16_t *__restrict__ out, size_t rows,
+                                      uint32_t k) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint32_t groups = k / 4;
+    if (i >= rows * groups) return;
+    const size_t row = i / groups;
+    const uint32_t c = uint32_t(i % groups) * 4;
+    const float4 v = *reinterpret_cast<const float4 *>(in + row * k + c);
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    uint16_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        hi[j] = h3b_narrow(x[j]);
+        lo[j] = h3b_narrow(x[j] - h3b_widen(hi[j]));
+    }
+    const uint2 h = make_uint2(uint32_t(hi[0]) | uint32_t(hi[1]) << 16, uint32_t(hi[2]) | uint32_t(hi[3]) << 16);
+    const uint2 l = make_uint2(uint32_t(lo[0]) | uint32_t(lo[1]) << 16, uint32_t(lo[2]) | uint32_t(lo[3]) << 16);
+    uint16_t *dst = out + row * 3 * size_t(k) + c;
+    *reinterpret_cast<uint2 *>(dst) = h;
+    *reinterpret_cast<uint2 *>(dst + k) = WEIGHT ? l : h;
+    *reinterpret_cast<uint2 *>(dst + 2 * size_t(k)) = WEIGHT ? h : l;
+}
+
+}  // namespace
+
+void h3b_f32_to_bf16_pad(h3_gpu *gpu, const float *in, uint16_t *out, size_t units, uint32_t dims,
+                         uint32_t padded) {
+    const size_t items = units * (padded / 4);
+    if (items)
+        h3b_f32_to_bf16_pad_kernel<<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, units, dims, padded);
+}
+
+void h3b_bf16_to_f32_unpad(h3_gpu *gpu, const uint16_t *in, float *out, size_t units, uint32_t dims,
+                           uint32_t padded) {
+    const size_t items = units * (dims / 4);
+    if (items)
+        h3b_bf16_to_f32_unpad_kernel<<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, units, dims, padded);
+}
+
+void h3b_split_bf16(h3_gpu *gpu, const float *in, uint16_t *out, size_t rows, uint32_t k, bool weight) {
+    const size_t items = rows * (k / 4);
+    if (!items) return;
+    if (weight) h3b_split_bf16_kernel<true><<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, rows, k);
+    else h3b_split_bf16_kernel<false><<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, rows, k);
+}
+
+/* ================================================================= C ABI */
+
+extern "C" int h3_gpu_rms_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                                   const h3_gpu_tensor *weight, uint32_t rows, uint32_t width,
+                                   float epsilon) {
+    const size_t count = size_t(rows) * width;
+    if (!h3b_need(gpu, input, H3_GPU_F32, count, "RMSNorm input") ||
+        !h3b_need(gpu, weight, H3_GPU_F32, width, "RMSNorm weight") ||
+        !h3b_need(gpu, output, H3_GPU_F32, count, "RMSNorm output") || !h3b_need_command(gpu))
+        return 0;
+    if (count) {
+        const float *x = h3b_ptr<float>(input), *w = h3b_ptr<float>(weight);
+        float *y = h3b_ptr<float>(output);
+        if (width % 4 == 0 && aligned16({x, w, y}))
+            h3b_rms_norm_f32_kernel<true><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, y, width, epsilon);
+        else
+            h3b_rms_norm_f32_kernel<false><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, y, width, epsilon);
+    }
+    return h3b_launched(gpu, "rms_norm_f32");
+}
+
+extern "C" int h3_gpu_layer_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                                     const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                                     uint32_t rows, uint32_t width, float epsilon) {
+    const size_t count = size_t(rows) * width;
+    if (!h3b_need(gpu, input, H3_GPU_F32, count, "LayerNorm input") ||
+        !h3b_need(gpu, weight, H3_GPU_F32, width, "LayerNorm weight") ||
+        !h3b_need(gpu, bias, H3_GPU_F32, width, "LayerNorm bias") ||
+        !h3b_need(gpu, output, H3_GPU_F32, count, "LayerNorm output") || !h3b_need_command(gpu))
+        return 0;
+    if (count) {
+        const float *x = h3b_ptr<float>(input), *w = h3b_ptr<float>(weight), *b = h3b_ptr<float>(bias);
+        float *y = h3b_ptr<float>(output);
+        if (width % 4 == 0 && aligned16({x, w, b, y}))
+            h3b_layer_norm_f32_kernel<true><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, b, y, width, epsilon);
+        else
+            h3b_layer_norm_f32_kernel<false><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, b, y, width, epsilon);
+    }
+    return h3b_launched(gpu, "layer_norm_f32");
+}
+
+extern "C" int h3_gpu_scale_add_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                                    const h3_gpu_tensor *branch, const h3_gpu_tensor *scale,
+                                    uint32_t rows, uint32_t width) {
+    const size_t count = size_t(rows) * width;
+    if (!h3b_need(gpu, residual, H3_GPU_F32, count, "scale-add residual") ||
+        !h3b_need(gpu, branch, H3_GPU_F32, count, "scale-add branch") ||
+        !h3b_need(gpu, scale, H3_GPU_F32, width, "scale-add scale") ||
+        !h3b_need(gpu, output, H3_GPU_F32, count, "scale-add output") || !h3b_need_command(gpu))
+        return 0;
+    if (count) {
+        const float *r = h3b_ptr<float>(residual), *b = h3b_ptr<float>(branch), *s = h3b_ptr<float>(scale);
+        float *y = h3b_ptr<float>(output);
+        if (width % 4 == 0 && aligned16({r, b, s, y}))
+            h3b_scale_add_f32_kernel<true><<<blocks_for(count / 4, 256), 256, 0, gpu->stream>>>(r, b, s, y, count / 4,
+                                                                                                  width);
+        else
+            h3b_scale_add_f32_kernel<false><<<blocks_for(count, 256), 256, 0, gpu->stream>>>(r, b, s, y, count, width);
+    }
+    return h3b_launched(gpu, "scale_add_f32");
+}
+
+extern "C" int h3_gpu_swiglu_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *fused,
+                                 uint32_t rows, uint32_t width) {
+    const size_t count = size_t(rows) * width;
+    if (!h3b_need(gpu, fused, H3_GPU_F32, count * 2, "SwiGLU input") ||
+        !h3b_need(gpu, output, H3_GPU_F32, count, "SwiGLU output") || !h3b_need_command(gpu))
+        return 0;
+    if (count) {
+        const float *f = h3b_ptr<float>(fused);
+        float *y = h3b_ptr<float>(output);
+        if (width % 4 == 0 && aligned16({f, y}))
+            h3b_swiglu_f32_kernel<true><<<blocks_for(count / 4, 256), 256, 0, gpu->stream>>>(f, y, count / 4, width);
+        else
+            h3b_swiglu_f32_kernel<false><<<blocks_for(count, 256), 256, 0, gpu->stream>>>(f, y, count, width);
+    }
+    return h3b_launched(gpu, "swiglu_f32");
+}
+
+extern "C" int h3_gpu_video_qkv_rope_f32(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                                         h3_gpu_tensor *value, const h3_gpu_tensor *qkv,
+                                         const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                         uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                                         uint32_t rope_half, float epsilon) {
+    const size_t count = size_t(sequence) * heads * head_dim;
+    const size_t rope_count = size_t(sequence) * rope_half;
+    if (!h3b_need(gpu, qkv, H3_GPU_F32, count * 3, "video QKV") ||
+        !h3b_need(gpu, rope_cos, H3_GPU_F32, rope_count, "video RoPE cosine") ||
+        !h3b_need(gpu, rope_sin, H3_GPU_F32, rope_count, "video RoPE sine") ||
+        !h3b_need(gpu, query, H3_GPU_F32, count, "video query") ||
+        !h3b_need(gpu, key, H3_GPU_F32, count, "video key") ||
+        !h3b_need(gpu, value, H3_GPU_F32, count, "video value"))
+        return 0;
+    if (rope_half * 2 > head_dim) return h3b_fail(gpu, "video RoPE spans more than the head dimension");
+    if (!h3b_need_command(gpu)) return 0;
+    if (count) {
+        const size_t threads = size_t(sequence) * heads * 32;
+        h3b_video_qkv_rope_f32_kernel<<<blocks_for(threads, 256), 256, 0, gpu->stream>>>(
+            h3b_ptr<float>(qkv), h3b_ptr<float>(rope_cos), h3b_ptr<float>(rope_sin), h3b_ptr<float>(query),
+            h3b_ptr<float>(key), h3b_ptr<float>(value), sequence, heads, head_dim, rope_half, epsilon);
+    }
+    return h3b_launched(gpu, "video_qkv_rope_f32");
+}

@@ -347,6 +347,28 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &args, uint32_t lane_
                                         packed[4 * v + 3]);
                         }
                     }
+                } else if (EPI == H3B_EPI_STORE_F32) {
+                    /* the accumulator as it is (+ F32 bias): `out` and `bias` point to F32 */
+                    float *dst = reinterpret_cast<float *>(args.out) + size_t(row) * args.out_cols + n_blk * BN;
+                    const float *bias = reinterpret_cast<const float *>(args.bias);
+    #pragma unroll 1
+                    for (int c = 0; c < BN / 32; c++) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_addr + c * 32, r);
+                        tmem_ld_wait();
+                        const uint32_t col0 = n_blk * BN + c * 32;
+    #pragma unroll
+                        for (int v = 0; v < 8; v++) {
+                            if (col0 + v * 4 >= args.out_cols) break;
+                            float4 value = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                            if (bias) {
+                                const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + col0 + v * 4));
+                                value.x += b.x; value.y += b.y; value.z += b.z; value.w += b.w;
+                            }
+                            if (row_ok) *reinterpret_cast<float4 *>(dst + c * 32 + v * 4) = value;
+                        }
+                    }
                 } else {
                     uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * BN;
     #pragma unroll 1
@@ -1014,6 +1036,29 @@ int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t 
     return h3b_launched(gpu, what, H3B_LINEAR);
 }
 
+int h3b_gemm_f32_split(h3_gpu *gpu, float *out, const float *x, const float *w, const float *bias,
+                       uint32_t rows, uint32_t k, uint32_t n) {
+    /* the reference sends an F32 projection to the tensor cores from a reduction length of
+     * 1,024 on (h3_cuda_gemm.cu:246-251); shorter ones stay exact */
+    if (!rows || !n || k < 1024 || k % 8 != 0 || n % 4 != 0 || env_flag("H3B_NO_TENSOR_CORES") ||
+        env_flag("H3B_F32_GEMM_EXACT") || !h3b_aligned16(out) || !h3b_aligned16(x) || !h3b_aligned16(w) ||
+        (bias && !h3b_aligned16(bias)))
+        return -1;
+    const size_t x_bytes = (size_t(rows) * 3 * k * sizeof(uint16_t) + 255) & ~size_t(255);
+    const size_t w_bytes = size_t(n) * 3 * k * sizeof(uint16_t);
+    uint8_t *scratch = static_cast<uint8_t *>(h3b_workspace(gpu, x_bytes + w_bytes));
+    if (!scratch) return h3b_fail(gpu, "linear_f32: cannot allocate the split operands");
+    uint16_t *x3 = reinterpret_cast<uint16_t *>(scratch), *w3 = reinterpret_cast<uint16_t *>(scratch + x_bytes);
+    h3b_split_bf16(gpu, x, x3, rows, k, false);
+    h3b_split_bf16(gpu, w, w3, n, k, true);
+    if (cudaGetLastError() != cudaSuccess) return h3b_fail(gpu, "linear_f32: operand split failed");
+    if (!launch_tc<H3B_EPI_STORE_F32>(gpu, reinterpret_cast<uint16_t *>(out), x3, w3,
+                                      reinterpret_cast<const uint16_t *>(bias), rows, 3 * k, n, n,
+                                      (n + BN - 1) / BN, 0))
+        return h3b_fail(gpu, "linear_f32: cannot set up the tensor-core GEMM (tensor map or launch attribute)");
+    return 1;
+}
+
 int h3b_qkv_rope_gemm(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, const uint16_t *x,
                       const uint16_t *w, const uint16_t *q_norm, const uint16_t *k_norm,
                       const uint16_t *rope_cos, const uint16_t *rope_sin, uint32_t rows,
@@ -1087,7 +1132,10 @@ extern "C" int h3_gpu_linear_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gp
         (bias && !h3b_need(gpu, bias, H3_GPU_F32, output_dim, "linear bias")) ||
         !h3b_need_command(gpu))
         return 0;
-    if (rows && output_dim)
+    const int served = h3b_gemm_f32_split(gpu, h3b_ptr<float>(output), h3b_ptr<float>(input), h3b_ptr<float>(weight),
+                                          bias ? h3b_ptr<float>(bias) : nullptr, rows, input_dim, output_dim);
+    if (served == 0) return 0;
+    if (served < 0 && rows && output_dim)
         launch_simt<float, float>(gpu, h3b_ptr<float>(input), h3b_ptr<float>(weight),
                                   bias ? h3b_ptr<float>(bias) : nullptr, h3b_ptr<float>(output),
                                   nullptr, rows, input_dim, output_dim);

@@ -89,26 +89,10 @@ extern "C" int h3_gpu_vae_encoder_group_norm_silu_f32(h3_gpu *gpu, h3_gpu_tensor
     h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t, uint32_t,
     uint32_t, uint32_t, uint32_t, float) { return off_path(gpu,
     "h3_gpu_vae_encoder_group_norm_silu_f32"); }
-extern "C" int h3_gpu_video_qkv_rope_f32(h3_gpu *gpu, h3_gpu_tensor *, h3_gpu_tensor *,
-    h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t,
-    uint32_t, uint32_t, uint32_t, float) { return off_path(gpu, "h3_gpu_video_qkv_rope_f32"); }
-extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *, const h3_gpu_tensor *, const
-    h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t, uint32_t, float) { return
-    off_path(gpu, "h3_gpu_sdpa_f32"); }
 extern "C" int h3_gpu_qkv_rope_f32(h3_gpu *gpu, h3_gpu_tensor *, h3_gpu_tensor *, h3_gpu_tensor *,
     const h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *,
     const h3_gpu_tensor *, uint32_t, uint32_t, uint32_t, uint32_t, float) { return off_path(gpu,
     "h3_gpu_qkv_rope_f32"); }
-extern "C" int h3_gpu_rms_norm_f32(h3_gpu *gpu, h3_gpu_tensor *, const h3_gpu_tensor *, const
-    h3_gpu_tensor *, uint32_t, uint32_t, float) { return off_path(gpu, "h3_gpu_rms_norm_f32"); }
-extern "C" int h3_gpu_layer_norm_f32(h3_gpu *gpu, h3_gpu_tensor *, const h3_gpu_tensor *, const
-    h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t, float) { return off_path(gpu,
-    "h3_gpu_layer_norm_f32"); }
-extern "C" int h3_gpu_scale_add_f32(h3_gpu *gpu, h3_gpu_tensor *, const h3_gpu_tensor *, const
-    h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t) { return off_path(gpu,
-    "h3_gpu_scale_add_f32"); }
-extern "C" int h3_gpu_swiglu_f32(h3_gpu *gpu, h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t,
-    uint32_t) { return off_path(gpu, "h3_gpu_swiglu_f32"); }
 extern "C" int h3_gpu_embedding_bf16(h3_gpu *gpu, h3_gpu_tensor *, const h3_gpu_tensor *, const
     h3_gpu_tensor *, uint32_t, uint32_t, uint32_t) { return off_path(gpu, "h3_gpu_embedding_bf16");
     }

@@ -212,6 +212,40 @@ int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *output,
                                        const h3_gpu_tensor *value, uint32_t sequence,
                                        uint32_t heads, uint32_t head_dim, float scale);
 
+/* ---- F32 operations of the video-VAE decoder's transformer, the step after the DiT
+ *      (h3_video_vae.c:425-461 run_block, 492-519 run_decoder): h3_gpu.h:150-197;
+ *      h3_cuda_core.cu:57-66,92-103,161-182,212-250,609-628,673-684,720-772;
+ *      h3_cuda_attention.cu:125-170,2657-2682,2990-3013,3125-3131.
+ *      Together with h3_gpu_linear_f32 above and the tensor / copy calls they are every device
+ *      call that file makes. Row ops are F32 throughout; the projections (reduction >= 1024)
+ *      run on the BF16 tensor cores as hi/lo splits where the reference uses TF32; attention
+ *      with head_dim 64 or 128 rounds q, k, v to BF16 as the reference does. -- */
+/* y = x * rsqrt(mean(x^2) + eps) * weight */
+int h3_gpu_rms_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                        const h3_gpu_tensor *weight, uint32_t rows, uint32_t width, float epsilon);
+/* y = (x - mean) * rsqrt(var + eps) * weight + bias */
+int h3_gpu_layer_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                          const h3_gpu_tensor *weight, const h3_gpu_tensor *bias, uint32_t rows,
+                          uint32_t width, float epsilon);
+/* out = residual + branch * scale[column] */
+int h3_gpu_scale_add_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                         const h3_gpu_tensor *branch, const h3_gpu_tensor *scale, uint32_t rows,
+                         uint32_t width);
+/* fused rows are [gate (width) | up (width)]; out = gate / (1 + exp(-gate)) * up */
+int h3_gpu_swiglu_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *fused,
+                      uint32_t rows, uint32_t width);
+/* fused rows are [head][q | k | v][head_dim]; q, k: unweighted RMS norm over the head, then RoPE
+ * on dims [0, 2 * rope_half) with pairs (d, d + rope_half); v copied. Tables [row][rope_half]. */
+int h3_gpu_video_qkv_rope_f32(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                              h3_gpu_tensor *value, const h3_gpu_tensor *qkv,
+                              const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                              uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                              uint32_t rope_half, float epsilon);
+/* non-causal attention, F32 tensors [row][head][head_dim] */
+int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                    const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t sequence,
+                    uint32_t heads, uint32_t head_dim, float scale);
+
 /* ---- elementwise / row ops: h3_gpu.h:136-149,365-370,515-517,551-556,616-622;
  *      h3_cuda_core.cu:15-210, h3_gpu_cuda.cu:937-1030, h3_cuda_dit.cu:536-548 -- */
 int h3_gpu_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *fused,

@@ -75,21 +75,9 @@ int h3_gpu_vae_encoder_pad_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *,
 int h3_gpu_vae_encoder_group_norm_silu_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, const
     h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t,
     uint32_t, float);
-int h3_gpu_video_qkv_rope_f32(h3_gpu *, h3_gpu_tensor *, h3_gpu_tensor *, h3_gpu_tensor *, const
-    h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t, uint32_t,
-    uint32_t, float);
-int h3_gpu_sdpa_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, const
-    h3_gpu_tensor *, uint32_t, uint32_t, uint32_t, float);
 int h3_gpu_qkv_rope_f32(h3_gpu *, h3_gpu_tensor *, h3_gpu_tensor *, h3_gpu_tensor *, const
     h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *, const
     h3_gpu_tensor *, uint32_t, uint32_t, uint32_t, uint32_t, float);
-int h3_gpu_rms_norm_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *,
-    uint32_t, uint32_t, float);
-int h3_gpu_layer_norm_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *,
-    const h3_gpu_tensor *, uint32_t, uint32_t, float);
-int h3_gpu_scale_add_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *,
-    const h3_gpu_tensor *, uint32_t, uint32_t);
-int h3_gpu_swiglu_f32(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, uint32_t);
 int h3_gpu_embedding_bf16(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, const h3_gpu_tensor *,
     uint32_t, uint32_t, uint32_t);
 int h3_gpu_gelu_bf16(h3_gpu *, h3_gpu_tensor *, const h3_gpu_tensor *, uint32_t, int);

@@ -729,3 +729,123 @@ void h3o_dit_block(uint16_t *hidden, const h3o_block_weights *w,
 
     free(mod); free(qkv); free(q); free(k); free(v); free(attn); free(branch);
 }
+
+/* ------------------------------------- video-VAE decoder F32 row operations */
+
+void h3o_rms_norm_f32(float *out, const float *in, const float *weight,
+                      uint32_t rows, uint32_t width, float eps) {
+    for (uint32_t r = 0; r < rows; r++) {
+        const float *x = in + (size_t)r * width;
+        float ss = 0.0f;
+        for (uint32_t c = 0; c < width; c++) ss += x[c] * x[c];
+        float inv = 1.0f / sqrtf(ss / (float)width + eps);
+        for (uint32_t c = 0; c < width; c++)
+            out[(size_t)r * width + c] = x[c] * inv * weight[c];
+    }
+}
+
+void h3o_layer_norm_f32(float *out, const float *in, const float *weight,
+                        const float *bias, uint32_t rows, uint32_t width, float eps) {
+    for (uint32_t r = 0; r < rows; r++) {
+        const float *x = in + (size_t)r * width;
+        float sum = 0.0f;
+        for (uint32_t c = 0; c < width; c++) sum += x[c];
+        float mean = sum / (float)width;
+        float vs = 0.0f;
+        for (uint32_t c = 0; c < width; c++) {
+            float d = x[c] - mean;
+            vs += d * d;
+        }
+        float inv = 1.0f / sqrtf(vs / (float)width + eps);
+        for (uint32_t c = 0; c < width; c++)
+            out[(size_t)r * width + c] = (x[c] - mean) * inv * weight[c] + bias[c];
+    }
+}
+
+void h3o_scale_add_f32(float *out, const float *residual, const float *branch,
+                       const float *scale, uint32_t rows, uint32_t width) {
+    for (uint32_t r = 0; r < rows; r++)
+        for (uint32_t c = 0; c < width; c++) {
+            size_t i = (size_t)r * width + c;
+            out[i] = residual[i] + branch[i] * scale[c];
+        }
+}
+
+void h3o_swiglu_f32(float *out, const float *fused, uint32_t rows, uint32_t width) {
+    for (uint32_t r = 0; r < rows; r++)
+        for (uint32_t c = 0; c < width; c++) {
+            float gate = fused[(size_t)r * width * 2 + c];
+            float up = fused[(size_t)r * width * 2 + width + c];
+            out[(size_t)r * width + c] = gate / (1.0f + expf(-gate)) * up;
+        }
+}
+
+void h3o_video_qkv_rope_f32(float *q, float *k, float *v, const float *qkv,
+                            const float *rope_cos, const float *rope_sin,
+                            uint32_t seq, uint32_t heads, uint32_t hd,
+                            uint32_t rope_half, float eps) {
+    for (uint32_t row = 0; row < seq; row++)
+        for (uint32_t head = 0; head < heads; head++) {
+            size_t unit = (size_t)row * heads + head;
+            const float *qi = qkv + unit * hd * 3, *ki = qi + hd, *vi = ki + hd;
+            float qs = 0.0f, ks = 0.0f;
+            for (uint32_t d = 0; d < hd; d++) {
+                qs = fmaf(qi[d], qi[d], qs);
+                ks = fmaf(ki[d], ki[d], ks);
+            }
+            float q_inv = 1.0f / sqrtf(qs / (float)hd + eps);
+            float k_inv = 1.0f / sqrtf(ks / (float)hd + eps);
+            for (uint32_t dim = 0; dim < hd; dim++) {
+                float q0 = qi[dim] * q_inv, k0 = ki[dim] * k_inv;
+                if (dim < rope_half) {
+                    uint32_t pair = dim + rope_half;
+                    float q1 = qi[pair] * q_inv, k1 = ki[pair] * k_inv;
+                    float c = rope_cos[(size_t)row * rope_half + dim];
+                    float s = rope_sin[(size_t)row * rope_half + dim];
+                    q0 = q0 * c - q1 * s;
+                    k0 = k0 * c - k1 * s;
+                } else if (dim < rope_half * 2) {
+                    uint32_t pair = dim - rope_half;
+                    float q1 = qi[pair] * q_inv, k1 = ki[pair] * k_inv;
+                    float c = rope_cos[(size_t)row * rope_half + pair];
+                    float s = rope_sin[(size_t)row * rope_half + pair];
+                    q0 = q0 * c + q1 * s;
+                    k0 = k0 * c + k1 * s;
+                }
+                q[unit * hd + dim] = q0;
+                k[unit * hd + dim] = k0;
+                v[unit * hd + dim] = vi[dim];
+            }
+        }
+}
+
+void h3o_sdpa_f32(float *out, const float *q, const float *k, const float *v,
+                  uint32_t seq, uint32_t heads, uint32_t hd, float scale) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (uint32_t h = 0; h < heads; h++)
+        for (uint32_t i = 0; i < seq; i++) {
+            float *scores = (float *)malloc((size_t)seq * sizeof(float));
+            const float *qp = q + ((size_t)i * heads + h) * hd;
+            float mx = -INFINITY;
+            for (uint32_t j = 0; j < seq; j++) {
+                const float *kp = k + ((size_t)j * heads + h) * hd;
+                float dot = 0.0f;
+                for (uint32_t d = 0; d < hd; d++) dot = fmaf(qp[d], kp[d], dot);
+                scores[j] = dot * scale;
+                if (scores[j] > mx) mx = scores[j];
+            }
+            float sum = 0.0f;
+            for (uint32_t j = 0; j < seq; j++) {
+                scores[j] = expf(scores[j] - mx);
+                sum += scores[j];
+            }
+            float inv = 1.0f / sum;
+            for (uint32_t d = 0; d < hd; d++) {
+                float acc = 0.0f;
+                for (uint32_t j = 0; j < seq; j++)
+                    acc = fmaf(scores[j] * inv, v[((size_t)j * heads + h) * hd + d], acc);
+                out[((size_t)i * heads + h) * hd + d] = acc;
+            }
+            free(scores);
+        }
+}

@@ -201,6 +201,28 @@ void h3o_dit_block(uint16_t *hidden, const h3o_block_weights *w,
                    uint16_t *dump_mod_attention, uint16_t *dump_attention,
                    uint16_t *dump_attention_output, uint16_t *dump_mod_mlp);
 
+/* ---- F32 operations of the video-VAE decoder's transformer (h3_video_vae.c:425-461). Each
+ * restates the CPU reference the reference's own tests check its kernels against. ---------- */
+/* tests/test_cuda_core.c:419-428 */
+void h3o_rms_norm_f32(float *out, const float *in, const float *weight,
+                      uint32_t rows, uint32_t width, float eps);
+/* tests/test_cuda_core.c:466-482 */
+void h3o_layer_norm_f32(float *out, const float *in, const float *weight,
+                        const float *bias, uint32_t rows, uint32_t width, float eps);
+/* tests/test_cuda_core.c:296-299 */
+void h3o_scale_add_f32(float *out, const float *residual, const float *branch,
+                       const float *scale, uint32_t rows, uint32_t width);
+/* tests/test_cuda_core.c:351-359 */
+void h3o_swiglu_f32(float *out, const float *fused, uint32_t rows, uint32_t width);
+/* tests/test_cuda_attention.c:120-185 with grouped = 1, weighted = 0 */
+void h3o_video_qkv_rope_f32(float *q, float *k, float *v, const float *qkv,
+                            const float *rope_cos, const float *rope_sin,
+                            uint32_t seq, uint32_t heads, uint32_t hd,
+                            uint32_t rope_half, float eps);
+/* tests/test_cuda_attention.c:204-242 (non-causal, [row][head][dim] output) */
+void h3o_sdpa_f32(float *out, const float *q, const float *k, const float *v,
+                  uint32_t seq, uint32_t heads, uint32_t hd, float scale);
+
 int h3o_threads(void);
 /* OpenMP threads used from now on (a launcher may have exported OMP_NUM_THREADS=1) */
 void h3o_set_threads(int count);

@@ -223,6 +223,43 @@ def sdpa_bf16_sparse(q, k, v, seq, heads, hd, scale, sparse_ptr, sparse_idx, hea
     return out
 
 
+def rms_norm_f32(x, weight, rows, width, eps=1e-5):
+    out = np.empty(rows * width, np.float32)
+    lib().h3o_rms_norm_f32(_p(out), _p(x), _p(weight), u32(rows), u32(width), f32(eps))
+    return out
+
+
+def layer_norm_f32(x, weight, bias, rows, width, eps=1e-5):
+    out = np.empty(rows * width, np.float32)
+    lib().h3o_layer_norm_f32(_p(out), _p(x), _p(weight), _p(bias), u32(rows), u32(width), f32(eps))
+    return out
+
+
+def scale_add_f32(residual, branch, scale, rows, width):
+    out = np.empty(rows * width, np.float32)
+    lib().h3o_scale_add_f32(_p(out), _p(residual), _p(branch), _p(scale), u32(rows), u32(width))
+    return out
+
+
+def swiglu_f32(fused, rows, width):
+    out = np.empty(rows * width, np.float32)
+    lib().h3o_swiglu_f32(_p(out), _p(fused), u32(rows), u32(width))
+    return out
+
+
+def video_qkv_rope_f32(qkv, cos, sin, seq, heads, hd, rope_half, eps=1e-5):
+    q, k, v = (np.empty(seq * heads * hd, np.float32) for _ in range(3))
+    lib().h3o_video_qkv_rope_f32(_p(q), _p(k), _p(v), _p(qkv), _p(cos), _p(sin), u32(seq), u32(heads),
+                                 u32(hd), u32(rope_half), f32(eps))
+    return q, k, v
+
+
+def sdpa_f32(q, k, v, seq, heads, hd, scale):
+    out = np.empty(seq * heads * hd, np.float32)
+    lib().h3o_sdpa_f32(_p(out), _p(q), _p(k), _p(v), u32(seq), u32(heads), u32(hd), f32(scale))
+    return out
+
+
 def patch_linear_bf16(out, x, weight, bias, row_map, offset_rows, rows, in_dim, out_dim):
     lib().h3o_patch_linear_bf16(_p(out), _p(x), _p(weight), _p(bias), _p(row_map),
                                 u32(offset_rows), u32(rows), u32(in_dim), u32(out_dim))

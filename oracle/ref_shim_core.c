@@ -16,3 +16,14 @@ void refcpu_swiglu(const float *fused, float *out, uint32_t rows,
 }
 
 float refcpu_silu(float x) { return ref_silu(x); }
+
+/* F32 norms of the video-VAE decoder (tests/test_cuda_core.c ref_rms_norm, ref_layer_norm) */
+void refcpu_rms_norm(const float *in, const float *w, float *out, uint32_t rows,
+                     uint32_t width, float eps) {
+    ref_rms_norm(in, w, out, rows, width, eps);
+}
+
+void refcpu_layer_norm(const float *in, const float *w, const float *b, float *out,
+                       uint32_t rows, uint32_t width, float eps) {
+    ref_layer_norm(in, w, b, out, rows, width, eps);
+}

@@ -132,3 +132,50 @@ def test_sdpa(seq, heads, hd, head_major):
     # own flash tolerance 1e-3 + 1e-2*|ref| (tests/test_cuda_attention.c:112-114)
     rounded = o.from_bf16(o.sdpa_bf16(q, k, v, seq, heads, hd, scale, head_major, round_p=1))
     assert np.all(np.abs(rounded - theirs) <= 1e-3 + 1e-2 * np.abs(theirs))
+
+
+# ---- F32 operations of the video-VAE decoder ---------------------------------------------
+
+def bits(a):
+    return np.asarray(a, np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("rows,width", [(3, 8), (5, 2048), (2, 130)])
+def test_f32_norms(rows, width):
+    x, w, b = o.normal_f32(rows * width, 41, 0.0, 3.0), o.normal_f32(width, 42, 0.0, 2.0), o.normal_f32(width, 43)
+    theirs = np.empty(rows * width, np.float32)
+    ref.refcpu_rms_norm(p(x), p(w), p(theirs), u32(rows), u32(width), f32(1e-5))
+    assert np.array_equal(bits(o.rms_norm_f32(x, w, rows, width)), bits(theirs))
+    ref.refcpu_layer_norm(p(x), p(w), p(b), p(theirs), u32(rows), u32(width), f32(1e-5))
+    assert np.array_equal(bits(o.layer_norm_f32(x, w, b, rows, width)), bits(theirs))
+
+
+def test_f32_swiglu():
+    rows, width = 4, 96
+    fused = o.normal_f32(rows * width * 2, 44, 0.0, 4.0)
+    theirs = np.empty(rows * width, np.float32)
+    ref.refcpu_swiglu(p(fused), p(theirs), u32(rows), u32(width))
+    assert np.array_equal(bits(o.swiglu_f32(fused, rows, width)), bits(theirs))
+
+
+@pytest.mark.parametrize("seq,heads,hd,half", [(5, 3, 16, 6), (4, 32, 64, 24), (3, 2, 8, 0)])
+def test_video_qkv_rope_f32(seq, heads, hd, half):
+    qkv = o.normal_f32(seq * heads * hd * 3, 45, 0.0, 2.0)
+    cos, sin = o.normal_f32(max(seq * half, 1), 46), o.normal_f32(max(seq * half, 1), 47)
+    n = seq * heads * hd
+    tq, tk, tv = (np.empty(n, np.float32) for _ in range(3))
+    ref.refcpu_qkv_rope(p(qkv), None, None, p(cos), p(sin), p(tq), p(tk), p(tv), u32(seq), u32(heads),
+                        u32(hd), u32(half), C.c_int(1), C.c_int(0), f32(1e-5))
+    q, k, v = o.video_qkv_rope_f32(qkv, cos, sin, seq, heads, hd, half)
+    assert np.array_equal(bits(q), bits(tq)) and np.array_equal(bits(k), bits(tk))
+    assert np.array_equal(bits(v), bits(tv))
+
+
+@pytest.mark.parametrize("seq,heads,hd", [(5, 2, 8), (100, 3, 64)])
+def test_sdpa_f32(seq, heads, hd):
+    n = seq * heads * hd
+    q, k, v = o.normal_f32(n, 48), o.normal_f32(n, 49), o.normal_f32(n, 50)
+    theirs = np.empty(n, np.float32)
+    ref.refcpu_sdpa(p(q), p(k), p(v), p(theirs), u32(1), u32(seq), u32(heads), u32(hd), f32(0.7), C.c_int(0),
+                    C.c_int(0))
+    assert np.array_equal(bits(o.sdpa_f32(q, k, v, seq, heads, hd, 0.7)), bits(theirs))
