@@ -17,6 +17,8 @@ oracle/_ref/libh3ref.so        the reference's CUDA backend (h3_gpu_cuda.cu + h3
 oracle/_ref/test_cuda_dit_b200 the reference's own test program tests/test_cuda_dit.c,
                                linked against the B200 library instead of its backend.
 oracle/_ref/dit_host_b200      the reference's unmodified DiT host code (loader, schedule, text
+oracle/_ref/vae_host_b200      the reference's unmodified video-VAE decoder host + tests/vae_host_driver.c,
+oracle/_ref/vae_host_ref       linked against this library / against libh3ref.so
 oracle/_ref/dit_host_ref       refiner, run_block, samplers) + tests/dit_host_driver.c, linked
                                against the B200 library / against the reference's CUDA backend.
 
@@ -181,6 +183,44 @@ def build_ref_hosts(product_lib: Path) -> list[Path]:
     return built
 
 
+def build_ref_vae_hosts(product_lib: Path) -> list[Path]:
+    """The reference's own video-VAE decoder host (h3_video_vae.c with h3_weights.c and
+    h3_safetensors.c: loader, latent normalisation, RoPE, the 36-block decoder, tiling, temporal
+    chunks and blending), compiled unmodified from the reference tree, plus the small driver
+    tests/vae_host_driver.c, linked once against the B200 library and once against the
+    reference's CUDA backend."""
+    if not REF.is_dir() or not product_lib.exists():
+        return []
+    OUT.mkdir(exist_ok=True)
+    units = ["h3_video_vae.c", "h3_weights.c", "h3_safetensors.c"]
+    driver = REPO / "tests" / "vae_host_driver.c"
+    objects = []
+    for unit in units:
+        obj = OUT / ("host_" + Path(unit).stem + ".o")
+        if not newer(obj, [REF / unit]):
+            run(["gcc", "-std=c11", "-D_DEFAULT_SOURCE", "-DH3_BACKEND_CUDA", "-O2", "-w", "-I", REF,
+                 "-c", REF / unit, "-o", obj])
+        objects.append(obj)
+    driver_obj = OUT / "vae_host_driver.o"
+    if not newer(driver_obj, [driver]):
+        run(["gcc", "-std=c11", "-D_DEFAULT_SOURCE", "-O2", "-Wall", "-I", REF, "-c", driver, "-o", driver_obj])
+    built = []
+    target = OUT / "vae_host_b200"
+    if not newer(target, [*objects, driver_obj, product_lib]):
+        run(["gcc", "-o", target, driver_obj, *objects, "-L", product_lib.parent, "-lh3b200",
+             "-Wl,-rpath,$ORIGIN/../../h3.c_b200", "-lpthread", "-lm"])
+    built.append(target)
+    ref_lib = OUT / "libh3ref.so"
+    if ref_lib.exists():
+        target = OUT / "vae_host_ref"
+        if not newer(target, [*objects, driver_obj, ref_lib]):
+            run(["gcc", "-o", target, driver_obj, *objects, "-L", OUT, "-lh3ref",
+                 "-Wl,--allow-shlib-undefined", "-Wl,-rpath,$ORIGIN",
+                 f"-Wl,-rpath,{CUDA_HOME / 'lib64'}", "-lpthread", "-lm"])
+        built.append(target)
+    return built
+
+
 def main() -> int:
     build_oracle()
     build_ref_cpu()
@@ -188,6 +228,7 @@ def main() -> int:
         build_ref_cuda()
     build_ref_tests(REPO / "h3.c_b200" / "libh3b200.so")
     build_ref_hosts(REPO / "h3.c_b200" / "libh3b200.so")
+    build_ref_vae_hosts(REPO / "h3.c_b200" / "libh3b200.so")
     return 0
 
 
