@@ -1443,6 +1443,7 @@ extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
         !h3b_need(gpu, value, H3_GPU_F32, count, "SDPA value") ||
         !h3b_need(gpu, output, H3_GPU_F32, count, "SDPA output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     const char *exact = getenv("H3B_SDPA_F32_EXACT");
     const bool aligned = h3b_aligned16(query->data) && h3b_aligned16(key->data) &&
                          h3b_aligned16(value->data) && h3b_aligned16(output->data);

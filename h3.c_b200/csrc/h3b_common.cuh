@@ -23,7 +23,17 @@ struct h3_gpu_tensor {
     h3_gpu_dtype dtype;
     struct h3_gpu *owner;
     int external;  /* wraps caller-owned memory: never freed or cached */
+    /* F32 tensors created with contents (file loads, from_f32) may serve as projection weights:
+     * h3_gpu_linear_f32 keeps their rows as scaled FP16 + one F32 scale per row here (see
+     * h3b_gemm_f32_half). Dropped by h3b_written() whenever this library writes the tensor, and
+     * with the tensor. */
+    int keeps_half = 0;
+    void *half_rows = nullptr;      /* [rows][k] FP16, then rows F32 inverse scales */
+    size_t half_bytes = 0;
+    uint32_t half_k = 0;
 };
+/* the tensor's data is about to change: forget what was derived from it */
+void h3b_written(h3_gpu_tensor *tensor);
 
 /* Device-side status word written by kernels whose bounded waits expire. */
 enum : int {
@@ -207,16 +217,22 @@ int h3b_qkv_rope_launch(h3_gpu *gpu, uint16_t *q, uint16_t *k, uint16_t *v, cons
                         const uint16_t *rs, uint32_t seq, uint32_t heads, uint32_t hd,
                         uint32_t rope_half, int grouped, float eps);
 bool h3b_tensor_map_available();
-/* F32 projection on the BF16 tensor cores: C[rows,n] = X[rows,k] . W[n,k]^T (+bias), all F32 in
- * memory. X and W are split into BF16 pairs hi + lo and the three products hi.hi + hi.lo +
- * lo.hi are summed in the F32 accumulator by one GEMM over 3k (products carry ~16 mantissa
- * bits; the reference's route for the same call is TF32, 10 bits, h3_cuda_gemm.cu:242-254).
- * Returns -1 when the shape cannot take it (caller runs the exact F32 kernel). */
-int h3b_gemm_f32_split(h3_gpu *gpu, float *out, const float *x, const float *w, const float *bias,
-                       uint32_t rows, uint32_t k, uint32_t n);
+/* F32 projection on the 16-bit tensor cores: C[rows,n] = X[rows,k] . W[n,k]^T (+bias), all F32 in
+ * memory. Every row of X and of W is scaled by a power of two that brings its largest
+ * magnitude to [2^13, 2^14) and rounded to FP16 (10 mantissa bits, the same as the TF32 format the
+ * reference uses for this call, h3_cuda_gemm.cu:242-254, but rounded to nearest instead of
+ * truncated, and at twice TF32's tensor rate); the epilogue multiplies the F32 accumulator by the
+ * two inverse scales (exact) and adds the bias. The weight's FP16 rows are kept with the weight
+ * tensor when it was created with contents. Returns -1 when the shape cannot take this route
+ * (caller runs the exact F32 kernel). */
+int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tensor *weight,
+                      const float *bias, uint32_t rows, uint32_t k, uint32_t n);
+void *h3b_device_alloc(h3_gpu *gpu, size_t bytes);           /* the tensors' block cache */
+void h3b_device_release(h3_gpu *gpu, void *data, size_t bytes);
 /* conversion kernels (h3b_f32ops.cu) */
 void h3b_f32_to_bf16_pad(h3_gpu *gpu, const float *in, uint16_t *out, size_t units, uint32_t dims,
                          uint32_t padded);
 void h3b_bf16_to_f32_unpad(h3_gpu *gpu, const uint16_t *in, float *out, size_t units, uint32_t dims,
                            uint32_t padded);
-void h3b_split_bf16(h3_gpu *gpu, const float *in, uint16_t *out, size_t rows, uint32_t k, bool weight);
+/* F32 [rows][k] -> FP16 [rows][k] scaled per row by a power of two, inverse scales to `inverse` */
+void h3b_scale_rows_f16(h3_gpu *gpu, const float *in, uint16_t *out, float *inverse, size_t rows, uint32_t k);

@@ -137,6 +137,30 @@ static void cache_release(h3_gpu *gpu, void *data, size_t bytes) {
     gpu->cache_bytes += bytes;
 }
 
+void *h3b_device_alloc(h3_gpu *gpu, size_t bytes) {
+    void *data = nullptr;
+    if (cache_alloc(gpu, (bytes + 255) & ~size_t(255), &data) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return data;
+}
+
+void h3b_device_release(h3_gpu *gpu, void *data, size_t bytes) {
+    if (data) cache_release(gpu, data, (bytes + 255) & ~size_t(255));
+}
+
+void h3b_written(h3_gpu_tensor *tensor) {
+    if (!tensor || !tensor->half_rows) return;
+    /* kernels that read the rows may still be queued: the block goes back to the stream-ordered
+     * cache, whose next user runs behind them */
+    if (tensor->owner) h3b_device_release(tensor->owner, tensor->half_rows, tensor->half_bytes);
+    else cudaFree(tensor->half_rows);
+    tensor->half_rows = nullptr;
+    tensor->half_bytes = 0;
+    tensor->half_k = 0;
+}
+
 void *h3b_workspace(h3_gpu *gpu, size_t bytes) {
     if (!bytes) bytes = 1;
     if (gpu->workspace && bytes <= gpu->workspace_bytes) return gpu->workspace;
@@ -476,6 +500,7 @@ static h3_gpu_tensor *tensor_new(h3_gpu *gpu, const void *values, size_t element
     tensor->dtype = dtype;
     tensor->owner = gpu;
     tensor->external = 0;
+    tensor->keeps_half = values && dtype == H3_GPU_F32;
     if (values && bytes && !upload(gpu, tensor->data, values, bytes)) {
         h3b_fail(gpu, "tensor upload failed");
         cache_release(gpu, tensor->data, block);
@@ -530,6 +555,7 @@ extern "C" void *h3x_tensor_device_pointer(const h3_gpu_tensor *tensor) {
 extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *tensor) {
     if (!tensor) return;
     h3_gpu *owner = tensor->owner;
+    h3b_written(tensor);
     if (!tensor->external) {
         if (owner)
             owner->stats.live_bytes =
@@ -564,6 +590,7 @@ static int write_range(h3_gpu_tensor *t, h3_gpu_dtype dtype, size_t offset, cons
         elements > t->elements - offset)
         return 0;
     size_t item = h3b_item_size(dtype);
+    h3b_written(t);
     return upload(t->owner, static_cast<unsigned char *>(t->data) + offset * item, values,
                   elements * item);
 }
@@ -802,6 +829,7 @@ static h3_gpu_tensor *load_file(h3_gpu *gpu, const char *path, uint64_t offset, 
         h3_gpu_tensor_free(tensor);
         return nullptr;
     }
+    tensor->keeps_half = dtype == H3_GPU_F32;
     return tensor;
 }
 
@@ -868,6 +896,7 @@ extern "C" int h3_gpu_cast_bf16_to_f32(h3_gpu *gpu, h3_gpu_tensor *output,
     if (!h3b_need(gpu, input, H3_GPU_BF16, elements, "cast input") ||
         !h3b_need(gpu, output, H3_GPU_F32, elements, "cast output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     if (elements) {
         unsigned blocks = unsigned((size_t(elements) + 1023) / 1024);
         h3b_cast_bf16_f32<<<blocks, 256, 0, gpu->stream>>>(h3b_ptr<uint16_t>(input),
@@ -886,6 +915,7 @@ static int device_copy(h3_gpu *gpu, h3_gpu_tensor *dst, size_t dst_offset,
         return h3b_fail(gpu, "copy range is out of bounds");
     if (!h3b_need_command(gpu)) return 0;
     size_t item = h3b_item_size(dtype);
+    h3b_written(dst);
     if (elements) {
         cudaError_t status = cudaMemcpyAsync(
             static_cast<unsigned char *>(dst->data) + dst_offset * item,

@@ -11,9 +11,11 @@
  * third pass), everything F32 like the reference (its tests hold these to 1e-5).
  *
  * The same file holds the small conversion kernels the F32 attention and F32 projection
- * routes need (F32 -> BF16 with head padding, BF16 -> F32, F32 -> split BF16 triples).
+ * routes need (F32 -> BF16 with head padding, BF16 -> F32, F32 rows -> scaled FP16 rows).
  */
 #include "h3b_common.cuh"
+
+#include <cuda_fp16.h>
 
 #include <cmath>
 #include <initializer_list>
@@ -242,32 +244,40 @@ __global__ void h3b_bf16_to_f32_unpad_kernel(const uint16_t *__restrict__ in, fl
         make_float4(h3b_lo(v.x), h3b_hi(v.x), h3b_lo(v.y), h3b_hi(v.y));
 }
 
-/* F32 [rows][k] -> BF16 [rows][3k]: x = hi + lo with hi = bf16(x), lo = bf16(x - hi). The
- * activation side writes [hi | hi | lo], the weight side [hi | lo | hi], so that the dot product of
- * two such rows is hi.hi + hi.lo + lo.hi: every product of an F32 projection to ~2^-16, summed
- * in the tensor core's F32 accumulator. */
-template <bool WEIGHT>
-__global__ void h3b_split_bf16_kernel(const float *__restrict__ in, uint16_t *__restrict__ out, size_t rows,
-                                      uint32_t k) {
-    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    const uint32_t groups = k / 4;
-    if (i >= rows * groups) return;
-    const size_t row = i / groups;
-    const uint32_t c = uint32_t(i % groups) * 4;
-    const float4 v = *reinterpret_cast<const float4 *>(in + row * k + c);
-    const float x[4] = {v.x, v.y, v.z, v.w};
-    uint16_t hi[4], lo[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        hi[j] = h3b_narrow(x[j]);
-        lo[j] = h3b_narrow(x[j] - h3b_widen(hi[j]));
+/* F32 [rows][k] -> FP16 [rows][k], one CTA per row: the row is scaled by the power of two that
+ * brings its largest magnitude into [2^13, 2^14) (FP16 tops out at 65,504; values down to 2^-27 of
+ * the row's maximum stay normal numbers) and rounded to nearest; inverse[row] undoes the scale. */
+__global__ void __launch_bounds__(kRowThreads)
+h3b_scale_rows_f16_kernel(const float *__restrict__ in, uint16_t *__restrict__ out, float *__restrict__ inverse,
+                          uint32_t k) {
+    __shared__ float scratch[kRowThreads / 32];
+    const float *x = in + size_t(blockIdx.x) * k;
+    uint16_t *y = out + size_t(blockIdx.x) * k;
+    float local = 0.0f;
+    for (uint32_t i = threadIdx.x; i < k / 4; i += kRowThreads) {
+        const float4 v = reinterpret_cast<const float4 *>(x)[i];
+        local = fmaxf(fmaxf(local, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
     }
-    const uint2 h = make_uint2(uint32_t(hi[0]) | uint32_t(hi[1]) << 16, uint32_t(hi[2]) | uint32_t(hi[3]) << 16);
-    const uint2 l = make_uint2(uint32_t(lo[0]) | uint32_t(lo[1]) << 16, uint32_t(lo[2]) | uint32_t(lo[3]) << 16);
-    uint16_t *dst = out + row * 3 * size_t(k) + c;
-    *reinterpret_cast<uint2 *>(dst) = h;
-    *reinterpret_cast<uint2 *>(dst + k) = WEIGHT ? l : h;
-    *reinterpret_cast<uint2 *>(dst + 2 * size_t(k)) = WEIGHT ? h : l;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, o));
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = local;
+    __syncthreads();
+    float largest = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; w++) largest = fmaxf(largest, scratch[w]);
+    /* exponent field of the maximum (0 for zero / subnormal rows, 255 for inf / nan: both get scale 1) */
+    const int field = int((__float_as_uint(largest) >> 23) & 0xffu);
+    int scale_field = 127 + 13 - (field - 127);
+    if (field == 0 || field == 255) scale_field = 127;
+    scale_field = min(max(scale_field, 1), 253);
+    const float scale = __uint_as_float(uint32_t(scale_field) << 23);
+    if (threadIdx.x == 0) inverse[blockIdx.x] = __uint_as_float(uint32_t(254 - scale_field) << 23);
+    for (uint32_t i = threadIdx.x; i < k / 4; i += kRowThreads) {
+        const float4 v = reinterpret_cast<const float4 *>(x)[i];
+        const __half2 lo = __floats2half2_rn(v.x * scale, v.y * scale), hi = __floats2half2_rn(v.z * scale, v.w * scale);
+        reinterpret_cast<uint2 *>(y)[i] =
+            make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+    }
 }
 
 }  // namespace
@@ -286,11 +296,9 @@ void h3b_bf16_to_f32_unpad(h3_gpu *gpu, const uint16_t *in, float *out, size_t u
         h3b_bf16_to_f32_unpad_kernel<<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, units, dims, padded);
 }
 
-void h3b_split_bf16(h3_gpu *gpu, const float *in, uint16_t *out, size_t rows, uint32_t k, bool weight) {
-    const size_t items = rows * (k / 4);
-    if (!items) return;
-    if (weight) h3b_split_bf16_kernel<true><<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, rows, k);
-    else h3b_split_bf16_kernel<false><<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, rows, k);
+void h3b_scale_rows_f16(h3_gpu *gpu, const float *in, uint16_t *out, float *inverse, size_t rows, uint32_t k) {
+    if (rows && k)
+        h3b_scale_rows_f16_kernel<<<unsigned(rows), kRowThreads, 0, gpu->stream>>>(in, out, inverse, k);
 }
 
 /* ================================================================= C ABI */
@@ -303,6 +311,7 @@ extern "C" int h3_gpu_rms_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_
         !h3b_need(gpu, weight, H3_GPU_F32, width, "RMSNorm weight") ||
         !h3b_need(gpu, output, H3_GPU_F32, count, "RMSNorm output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     if (count) {
         const float *x = h3b_ptr<float>(input), *w = h3b_ptr<float>(weight);
         float *y = h3b_ptr<float>(output);
@@ -323,6 +332,7 @@ extern "C" int h3_gpu_layer_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h
         !h3b_need(gpu, bias, H3_GPU_F32, width, "LayerNorm bias") ||
         !h3b_need(gpu, output, H3_GPU_F32, count, "LayerNorm output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     if (count) {
         const float *x = h3b_ptr<float>(input), *w = h3b_ptr<float>(weight), *b = h3b_ptr<float>(bias);
         float *y = h3b_ptr<float>(output);
@@ -343,6 +353,7 @@ extern "C" int h3_gpu_scale_add_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3
         !h3b_need(gpu, scale, H3_GPU_F32, width, "scale-add scale") ||
         !h3b_need(gpu, output, H3_GPU_F32, count, "scale-add output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     if (count) {
         const float *r = h3b_ptr<float>(residual), *b = h3b_ptr<float>(branch), *s = h3b_ptr<float>(scale);
         float *y = h3b_ptr<float>(output);
@@ -361,6 +372,7 @@ extern "C" int h3_gpu_swiglu_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gp
     if (!h3b_need(gpu, fused, H3_GPU_F32, count * 2, "SwiGLU input") ||
         !h3b_need(gpu, output, H3_GPU_F32, count, "SwiGLU output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     if (count) {
         const float *f = h3b_ptr<float>(fused);
         float *y = h3b_ptr<float>(output);
@@ -388,6 +400,9 @@ extern "C" int h3_gpu_video_qkv_rope_f32(h3_gpu *gpu, h3_gpu_tensor *query, h3_g
         return 0;
     if (rope_half * 2 > head_dim) return h3b_fail(gpu, "video RoPE spans more than the head dimension");
     if (!h3b_need_command(gpu)) return 0;
+    h3b_written(query);
+    h3b_written(key);
+    h3b_written(value);
     if (count) {
         const size_t threads = size_t(sequence) * heads * 32;
         h3b_video_qkv_rope_f32_kernel<<<blocks_for(threads, 256), 256, 0, gpu->stream>>>(

@@ -61,6 +61,9 @@ constexpr size_t TC_SMEM_QKV = TC_SMEM + 4 * QKV_STAGE_BYTES;
 struct TcArgs {
     uint16_t *out;
     const uint16_t *bias;
+    /* F32-store epilogue: out and bias point to F32; the accumulator is multiplied by
+     * row_scale[row] * col_scale[column] first (either may be null) */
+    const float *row_scale, *col_scale;
     int *status;
     long long wait_cycles; /* budget of every bounded wait */
     uint32_t rows;        /* M */
@@ -89,6 +92,13 @@ struct TcArgs {
 };
 
 constexpr int ROPE_HALF = 48;   /* the model's RoPE width (h3_dit.c ROPE_HALF) */
+
+/* A and B are BF16 for every epilogue but the F32 store, whose operands are FP16 (format 0 in
+ * bits 7-9 and 10-12 of the instruction descriptor instead of 1) */
+template <int EPI>
+__host__ __device__ constexpr uint32_t operand_formats(uint32_t idesc) {
+    return EPI == H3B_EPI_STORE_F32 ? idesc & ~((7u << 7) | (7u << 10)) : idesc;
+}
 
 /* One 128-column unit of the grouped QKV row = q, k or v of one head, held by the thread
  * that owns the row: F32 accumulators -> BF16 (the reference rounds the projection first),
@@ -351,6 +361,7 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &args, uint32_t lane_
                     /* the accumulator as it is (+ F32 bias): `out` and `bias` point to F32 */
                     float *dst = reinterpret_cast<float *>(args.out) + size_t(row) * args.out_cols + n_blk * BN;
                     const float *bias = reinterpret_cast<const float *>(args.bias);
+                    const float row_scale = args.row_scale && row_ok ? args.row_scale[row] : 1.0f;
     #pragma unroll 1
                     for (int c = 0; c < BN / 32; c++) {
                         uint32_t r[32];
@@ -362,6 +373,11 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &args, uint32_t lane_
                             if (col0 + v * 4 >= args.out_cols) break;
                             float4 value = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
                                                        __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                            if (args.col_scale) {
+                                const float4 s = __ldg(reinterpret_cast<const float4 *>(args.col_scale + col0 + v * 4));
+                                value.x *= row_scale * s.x; value.y *= row_scale * s.y;
+                                value.z *= row_scale * s.z; value.w *= row_scale * s.w;
+                            }
                             if (bias) {
                                 const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + col0 + v * 4));
                                 value.x += b.x; value.y += b.y; value.z += b.z; value.w += b.w;
@@ -493,7 +509,7 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         /* ---- MMA issuer: all lanes run the loop (uniform operands), lane 0 issues ---- */
         {
             const uint32_t leader = lane == 0;
-            constexpr uint32_t idesc = instruction_desc(BM, BN);
+            constexpr uint32_t idesc = operand_formats<EPI>(instruction_desc(BM, BN));
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
@@ -665,7 +681,7 @@ h3b_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         /* ---- MMA issuer: the even CTA only ---- */
         if (rank == 0) {
             const uint32_t leader = lane == 0;
-            constexpr uint32_t idesc = instruction_desc(256, BN);
+            constexpr uint32_t idesc = operand_formats<EPI>(instruction_desc(256, BN));
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             const uint32_t a_lo0 = desc_lo_kmajor(a_smem), b_lo0 = desc_lo_kmajor(b_smem);
             bool alive = true;
@@ -1036,25 +1052,53 @@ int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t 
     return h3b_launched(gpu, what, H3B_LINEAR);
 }
 
-int h3b_gemm_f32_split(h3_gpu *gpu, float *out, const float *x, const float *w, const float *bias,
-                       uint32_t rows, uint32_t k, uint32_t n) {
+int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tensor *weight,
+                      const float *bias, uint32_t rows, uint32_t k, uint32_t n) {
     /* the reference sends an F32 projection to the tensor cores from a reduction length of
      * 1,024 on (h3_cuda_gemm.cu:246-251); shorter ones stay exact */
+    const float *w = h3b_ptr<float>(weight);
     if (!rows || !n || k < 1024 || k % 8 != 0 || n % 4 != 0 || env_flag("H3B_NO_TENSOR_CORES") ||
         env_flag("H3B_F32_GEMM_EXACT") || !h3b_aligned16(out) || !h3b_aligned16(x) || !h3b_aligned16(w) ||
         (bias && !h3b_aligned16(bias)))
         return -1;
-    const size_t x_bytes = (size_t(rows) * 3 * k * sizeof(uint16_t) + 255) & ~size_t(255);
-    const size_t w_bytes = size_t(n) * 3 * k * sizeof(uint16_t);
-    uint8_t *scratch = static_cast<uint8_t *>(h3b_workspace(gpu, x_bytes + w_bytes));
-    if (!scratch) return h3b_fail(gpu, "linear_f32: cannot allocate the split operands");
-    uint16_t *x3 = reinterpret_cast<uint16_t *>(scratch), *w3 = reinterpret_cast<uint16_t *>(scratch + x_bytes);
-    h3b_split_bf16(gpu, x, x3, rows, k, false);
-    h3b_split_bf16(gpu, w, w3, n, k, true);
-    if (cudaGetLastError() != cudaSuccess) return h3b_fail(gpu, "linear_f32: operand split failed");
-    if (!launch_tc<H3B_EPI_STORE_F32>(gpu, reinterpret_cast<uint16_t *>(out), x3, w3,
-                                      reinterpret_cast<const uint16_t *>(bias), rows, 3 * k, n, n,
-                                      (n + BN - 1) / BN, 0))
+    auto rounded = [](size_t bytes) { return (bytes + 255) & ~size_t(255); };
+    const size_t x_bytes = rounded(size_t(rows) * k * sizeof(uint16_t)), x_scale_bytes = rounded(size_t(rows) * sizeof(float));
+    const size_t w_bytes = rounded(size_t(n) * k * sizeof(uint16_t)), w_scale_bytes = rounded(size_t(n) * sizeof(float));
+    /* the weight's FP16 rows: kept with a tensor that was created with contents, else scratch */
+    h3_gpu_tensor *keeper = weight->keeps_half && !weight->external && weight->elements == size_t(n) * k
+                                ? const_cast<h3_gpu_tensor *>(weight) : nullptr;
+    uint8_t *scratch = static_cast<uint8_t *>(
+        h3b_workspace(gpu, x_bytes + x_scale_bytes + (keeper ? 0 : w_bytes + w_scale_bytes)));
+    if (!scratch) return h3b_fail(gpu, "linear_f32: cannot allocate the FP16 operands");
+    uint16_t *x16 = reinterpret_cast<uint16_t *>(scratch);
+    float *x_scale = reinterpret_cast<float *>(scratch + x_bytes);
+    uint16_t *w16;
+    float *w_scale;
+    if (keeper) {
+        if (!keeper->half_rows || keeper->half_k != k) {
+            h3b_written(keeper);
+            keeper->half_rows = h3b_device_alloc(gpu, w_bytes + w_scale_bytes);
+            if (!keeper->half_rows) return h3b_fail(gpu, "linear_f32: cannot allocate the weight's FP16 rows");
+            keeper->half_bytes = w_bytes + w_scale_bytes;
+            keeper->half_k = k;
+            h3b_scale_rows_f16(gpu, w, static_cast<uint16_t *>(keeper->half_rows),
+                               reinterpret_cast<float *>(static_cast<uint8_t *>(keeper->half_rows) + w_bytes), n, k);
+        }
+        w16 = static_cast<uint16_t *>(keeper->half_rows);
+        w_scale = reinterpret_cast<float *>(static_cast<uint8_t *>(keeper->half_rows) + w_bytes);
+    } else {
+        w16 = reinterpret_cast<uint16_t *>(scratch + x_bytes + x_scale_bytes);
+        w_scale = reinterpret_cast<float *>(scratch + x_bytes + x_scale_bytes + w_bytes);
+        h3b_scale_rows_f16(gpu, w, w16, w_scale, n, k);
+    }
+    h3b_scale_rows_f16(gpu, x, x16, x_scale, rows, k);
+    if (cudaGetLastError() != cudaSuccess) return h3b_fail(gpu, "linear_f32: operand conversion failed");
+    TcArgs extra = {};
+    extra.row_scale = x_scale;
+    extra.col_scale = w_scale;
+    if (!launch_tc<H3B_EPI_STORE_F32>(gpu, reinterpret_cast<uint16_t *>(out), x16, w16,
+                                      reinterpret_cast<const uint16_t *>(bias), rows, k, n, n,
+                                      (n + BN - 1) / BN, 0, &extra))
         return h3b_fail(gpu, "linear_f32: cannot set up the tensor-core GEMM (tensor map or launch attribute)");
     return 1;
 }
@@ -1132,8 +1176,9 @@ extern "C" int h3_gpu_linear_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gp
         (bias && !h3b_need(gpu, bias, H3_GPU_F32, output_dim, "linear bias")) ||
         !h3b_need_command(gpu))
         return 0;
-    const int served = h3b_gemm_f32_split(gpu, h3b_ptr<float>(output), h3b_ptr<float>(input), h3b_ptr<float>(weight),
-                                          bias ? h3b_ptr<float>(bias) : nullptr, rows, input_dim, output_dim);
+    h3b_written(output);
+    const int served = h3b_gemm_f32_half(gpu, h3b_ptr<float>(output), h3b_ptr<float>(input), weight,
+                                         bias ? h3b_ptr<float>(bias) : nullptr, rows, input_dim, output_dim);
     if (served == 0) return 0;
     if (served < 0 && rows && output_dim)
         launch_simt<float, float>(gpu, h3b_ptr<float>(input), h3b_ptr<float>(weight),

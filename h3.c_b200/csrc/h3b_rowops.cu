@@ -599,6 +599,7 @@ extern "C" int h3_gpu_adaln_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu
         !h3b_need(gpu, row_map, H3_GPU_U32, rows, "AdaLN row map") ||
         !h3b_need(gpu, output, H3_GPU_F32, count, "AdaLN output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(output);
     if (shift_slot >= slots || scale_slot >= slots)
         return h3b_fail(gpu, "AdaLN modulation slot is out of range");
     if (count)
@@ -664,6 +665,7 @@ extern "C" int h3_gpu_gate_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
                                const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
                                const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
                                uint32_t slots, uint32_t gate_slot) {
+    h3b_written(output);
     return gate_common<float>(gpu, output, residual, branch, modulation, row_map, rows, width,
                               slots, gate_slot, H3_GPU_F32, "gate_f32");
 }
@@ -916,6 +918,7 @@ extern "C" int h3_gpu_silu_f32(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_ten
     if (!h3b_need(gpu, in, H3_GPU_F32, n, "SiLU input") ||
         !h3b_need(gpu, out, H3_GPU_F32, n, "SiLU output") || !h3b_need_command(gpu))
         return 0;
+    h3b_written(out);
     if (n)
         h3b_silu_f32_kernel<<<blocks_for(n, 256), 256, 0, gpu->stream>>>(h3b_ptr<float>(in),
                                                                         h3b_ptr<float>(out), n);
@@ -953,6 +956,7 @@ extern "C" int h3_gpu_euler_bf16(h3_gpu *gpu, h3_gpu_tensor *sample, size_t samp
         !h3b_need(gpu, previous, H3_GPU_BF16, elements, "Euler previous velocity") ||
         !h3b_need_command(gpu))
         return 0;
+    h3b_written(sample);
     if (elements)
         h3b_euler_kernel<<<blocks_for(elements, 256), 256, 0, gpu->stream>>>(
             h3b_ptr<float>(sample, sample_offset), h3b_ptr<uint16_t>(last),

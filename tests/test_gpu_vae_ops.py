@@ -150,12 +150,60 @@ def test_linear_f32(gpu, pkg, rows, k, n, bias):
             + (b.astype(np.float64) if bias else 0.0)).reshape(-1)
     if k >= 1024:
         close(out.read(), want, 1e-2, 1e-3, what="linear_f32 (tensor-core route)")
-        # the hi/lo split keeps ~16 bits per product; what is left is the tensor core's F32
-        # accumulator, which truncates on every add (measured: -3.6e-5 relative after the 1,536
-        # accumulation steps of a reduction of 8,192): an order of magnitude inside the TF32 bar
-        close(out.read(), want, 2e-4, 2e-4, what="linear_f32 split precision")
+        # FP16 operands rounded to nearest carry 11 significant bits per factor: as a whole the result
+        # sits well inside what TF32 (10 bits, truncated) leaves
+        assert rel_l2(out.read(), want) < 5e-4
     else:
         close(out.read(), want, 1e-3, what="linear_f32 exact")
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+def test_linear_f32_rows_of_very_different_magnitude(gpu, pkg):
+    """Each row of X and of W is scaled by its own power of two before it is rounded to FP16, so rows
+    around 1e-20 and rows around 1e+15 in one call lose nothing (unscaled FP16 spans 6e-8 .. 65,504)."""
+    rows, k, n = 96, 1024, 64
+    x, w = nf(rows * k, 30).reshape(rows, k), nf(n * k, 31, 1.0 / np.sqrt(k)).reshape(n, k)
+    x *= np.float32(10.0) ** np.linspace(-20, 15, rows, dtype=np.float32)[:, None]
+    w *= np.float32(10.0) ** np.linspace(-12, 10, n, dtype=np.float32)[:, None]
+    tx, tw = gpu.f32(x), gpu.f32(w)
+    out = gpu.new(rows * n, pkg.F32)
+    run(gpu, lambda: gpu.op("linear_f32", out, tx, tw, None, rows, k, n))
+    got = out.read().reshape(rows, n).astype(np.float64)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.all(np.isfinite(got))
+    # against the sum of the products' magnitudes (a dot product itself may cancel to near zero):
+    # two factors of 11 significant bits each leave at most 2^-10 of it
+    budget = np.abs(x).astype(np.float64) @ np.abs(w).astype(np.float64).T
+    assert np.all(np.abs(got - want) <= 2.0 ** -10 * budget), float(np.max(np.abs(got - want) / budget))
+
+
+def test_linear_f32_forgets_the_weight_rows_when_the_weight_changes(gpu, pkg):
+    """A weight tensor created with contents keeps its FP16 rows between calls; writing the tensor
+    (host write, device copy, or as an op's output) drops them."""
+    rows, k, n = 64, 1024, 128
+    x, w1, w2 = nf(rows * k, 32), nf(n * k, 33, 0.03), nf(n * k, 34, 0.03)
+    tx, tw, tw2 = gpu.f32(x), gpu.f32(w1), gpu.f32(w2)
+    out = gpu.new(rows * n, pkg.F32)
+
+    def product(w):
+        return (x.reshape(rows, k).astype(np.float64) @ w.reshape(n, k).astype(np.float64).T).reshape(-1)
+    run(gpu, lambda: gpu.op("linear_f32", out, tx, tw, None, rows, k, n))
+    assert rel_l2(out.read(), product(w1)) < 5e-4
+    run(gpu, lambda: gpu.op("linear_f32", out, tx, tw, None, rows, k, n))          # from the kept rows
+    assert rel_l2(out.read(), product(w1)) < 5e-4
+    assert gpu.lib.h3_gpu_tensor_write_f32(tw.handle, w2.ctypes.data, w2.size) == 1
+    run(gpu, lambda: gpu.op("linear_f32", out, tx, tw, None, rows, k, n))
+    assert rel_l2(out.read(), product(w2)) < 5e-4
+    run(gpu, lambda: gpu.op("copy_f32", tw, 0, gpu.f32(w1), 0, w1.size))
+    run(gpu, lambda: gpu.op("linear_f32", out, tx, tw, None, rows, k, n))
+    assert rel_l2(out.read(), product(w1)) < 5e-4
+    run(gpu, lambda: gpu.op("scale_add_f32", tw, tw2, tw2, gpu.f32(np.zeros(k, np.float32)), n, k))   # tw = w2
+    run(gpu, lambda: gpu.op("linear_f32", out, tx, tw, None, rows, k, n))
+    assert rel_l2(out.read(), product(w2)) < 5e-4
 
 
 def decoder_block_weights(seed):
@@ -210,11 +258,6 @@ def oracle_decoder_block(w, hidden, cos, sin, rows):
     act = o.swiglu_f32(ff1, rows, FFN)
     branch = o.linear_f32(act, w["w2"], w["w2_b"], rows, FFN, HIDDEN)
     return o.scale_add_f32(hidden, branch, w["scale2"], rows, HIDDEN)
-
-
-def rel_l2(a, b):
-    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
-    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
 
 
 def test_decoder_block_matches_oracle(gpu, pkg):
