@@ -47,6 +47,7 @@ WORKLOADS = {
                        "cond/uncond on two GPU groups, 50 blocks"),
     "c5small": (256, 6144, "512x512x22f (S=6,400), 20 Euler steps with classifier-free guidance, "
                            "cond/uncond on two GPU groups, 50 blocks"),
+    "vae_tile": (0, 1797, "one tile of the video-VAE decoder (the step after the DiT): metric vae_tile_decode_ms"),
 }
 
 
@@ -935,6 +936,276 @@ def run_cfg_arm(args, shape, sequence, text_rows):
     gpu.close()
 
 
+# ------------------------------------------------------------- video-VAE decoder tile
+
+VAE = dict(latent=24, hidden=2048, layers=36, heads=32, head_dim=64, ffn=8192, rope_half=24,
+           output_patch=3 * 4 * 16 * 16, registers=4, suffix=5)
+VAE_TILE_ROWS = 7 * 16 * 16 + 5     # one 256-pixel tile of seven latent frames (h3_video_vae.c:1013-1019)
+
+
+def vae_cpu_sample(rows=VAE_TILE_ROWS, gemm_rows=128, attn_rows=256):
+    """The oracle port on a bounded sample of one decoder block, extrapolated linearly to a tile
+    decode (36 blocks): (ms per tile, description, threads, seconds spent)."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import h3_oracle as o
+    o.set_threads(len(os.sched_getaffinity(0)))
+    v, rng = VAE, np.random.default_rng(0)
+    inner = v["heads"] * v["head_dim"]
+
+    def rand(n, std=1.0):
+        return rng.standard_normal(n, dtype=np.float32) * np.float32(std)
+    x = rand(gemm_rows * v["hidden"])
+    ones, scale = np.ones(v["hidden"], np.float32), np.full(v["hidden"], 0.25, np.float32)
+    w_qkv, w_out = rand(3 * inner * v["hidden"], 0.02), rand(v["hidden"] * inner, 0.02)
+    w1, w2 = rand(2 * v["ffn"] * v["hidden"], 0.02), rand(v["hidden"] * v["ffn"], 0.02)
+    cos, sin = rand(gemm_rows * v["rope_half"]), rand(gemm_rows * v["rope_half"])
+    t0 = time.perf_counter()
+    n1 = o.rms_norm_f32(x, ones, gemm_rows, v["hidden"])
+    qkv = o.linear_f32(n1, w_qkv, None, gemm_rows, v["hidden"], 3 * inner)
+    q, _, _ = o.video_qkv_rope_f32(qkv, cos, sin, gemm_rows, v["heads"], v["head_dim"], v["rope_half"])
+    br = o.linear_f32(q, w_out, None, gemm_rows, inner, v["hidden"])
+    x = o.scale_add_f32(x, br, scale, gemm_rows, v["hidden"])
+    n2 = o.rms_norm_f32(x, ones, gemm_rows, v["hidden"])
+    act = o.swiglu_f32(o.linear_f32(n2, w1, None, gemm_rows, v["hidden"], 2 * v["ffn"]), gemm_rows, v["ffn"])
+    o.scale_add_f32(x, o.linear_f32(act, w2, None, gemm_rows, v["ffn"], v["hidden"]), scale, gemm_rows, v["hidden"])
+    t_rows = time.perf_counter() - t0
+    # attention is quadratic: all keys, a slice of the query rows, by running the oracle on the first
+    # attn_rows rows of a problem whose keys are the full tile (cost is linear in query rows)
+    n = rows * inner
+    qa, ka, va = rand(n), rand(n), rand(n)
+    t0 = time.perf_counter()
+    o.sdpa_f32(qa[:attn_rows * inner], ka, va, attn_rows, v["heads"], v["head_dim"], 0.125)
+    t_attn = (time.perf_counter() - t0) * rows / attn_rows    # attn_rows x attn_rows -> attn_rows x rows keys
+    block_s = t_rows * rows / gemm_rows + t_attn * rows / attn_rows
+    desc = (f"one decoder block: projections + row ops on {gemm_rows} of {rows} rows, attention on {attn_rows} x "
+            f"{attn_rows} rows scaled to {rows} x {rows}; extrapolated linearly to {v['layers']} blocks")
+    return block_s * v["layers"] * 1e3, desc, o.threads(), t_rows + t_attn
+
+
+def run_vae_reference_arm(args):
+    """The CPU arm for the VAE tile: the oracle port on the host cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    values, desc, threads = [], "", 1
+    for i in range(args.warmup + args.steps):
+        ms, desc, threads, _ = vae_cpu_sample(gemm_rows=64, attn_rows=128)
+        if i >= args.warmup:
+            values.append(ms)
+    value = statistics.mean(values)
+    line = {"impl": "reference", "metric": "vae_tile_decode_ms", "value": value, "unit": "ms/tile", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "vae_tile: " + WORKLOADS["vae_tile"][2], "rows": VAE_TILE_ROWS, "blocks": VAE["layers"]},
+            "cpu_baseline": {"value": value, "unit": "ms/tile", "cores": threads, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": "ms/tile", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_vae_arm(args):
+    """One tile of the video-VAE decoder (the step after the DiT on the reference's pipeline): the op
+    sequence of run_resident_tile / run_block (h3_video_vae.c:425-461, 600-660) on 1,797 rows with
+    all 36 blocks' F32 weights resident (9.7 GB), through the C ABI."""
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    from h3c_b200.plumbing import TorchMemory
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    gpu = pkg.Gpu(local_rank)
+    mem, peaks, rows = TorchMemory(torch, gpu, device), measured_peaks(), VAE_TILE_ROWS
+    v = dict(VAE, layers=min(args.blocks, VAE["layers"]))       # --blocks 1: a small case for profiler captures
+    inner, patches = v["heads"] * v["head_dim"], VAE_TILE_ROWS - v["suffix"]
+    generator = torch.Generator(device=device).manual_seed(0)
+
+    def weight(n, std=0.02, fill=None):
+        t = mem.f32(n, std=None if fill is not None else std, generator=generator)
+        if fill is not None:
+            mem.torch_of(t).fill_(fill)
+        gpu.lib.h3x_tensor_keep_half_rows(t.handle, 1)
+        return t
+    blocks = [dict(norm1=weight(v["hidden"], fill=1.0), qkv_w=weight(3 * inner * v["hidden"]), qkv_b=weight(3 * inner),
+                   out_w=weight(v["hidden"] * inner), out_b=weight(v["hidden"]), scale1=weight(v["hidden"], fill=0.25),
+                   norm2=weight(v["hidden"], fill=1.0), w1=weight(2 * v["ffn"] * v["hidden"]), w1_b=weight(2 * v["ffn"]),
+                   w2=weight(v["hidden"] * v["ffn"]), w2_b=weight(v["hidden"]), scale2=weight(v["hidden"], fill=0.25))
+              for _ in range(v["layers"])]
+    post_w, post_b = weight(v["latent"] ** 2, 0.2), weight(v["latent"])
+    embed_w, embed_b = weight(v["hidden"] * v["latent"], 0.2), weight(v["hidden"])
+    registers, zero = weight(v["registers"] * v["hidden"], 1.0), weight(v["hidden"], fill=0.0)
+    norm_out_w, norm_out_b = weight(v["hidden"], fill=1.0), weight(v["hidden"])
+    proj_w, proj_b = weight(v["output_patch"] * v["hidden"]), weight(v["output_patch"])
+    act = {name: mem.f32(n) for name, n in dict(
+        latent=patches * v["latent"], post=patches * v["latent"], patch_hidden=patches * v["hidden"],
+        hidden=rows * v["hidden"], norm=rows * v["hidden"], qkv=rows * inner * 3, query=rows * inner, key=rows * inner,
+        value=rows * inner, heads=rows * inner, branch=rows * v["hidden"], ff1=rows * v["ffn"] * 2,
+        activated=rows * v["ffn"], projected=rows * v["output_patch"]).items()}
+    angle = torch.randn(rows * v["rope_half"], device=device, generator=generator) * 2.0
+    rope_cos, rope_sin = mem.f32(rows * v["rope_half"]), mem.f32(rows * v["rope_half"])
+    mem.torch_of(rope_cos).copy_(angle.cos())
+    mem.torch_of(rope_sin).copy_(angle.sin())
+    host_latent = torch.randn(patches * v["latent"], generator=torch.Generator().manual_seed(1)).pin_memory()
+    host_out = torch.empty(rows * v["output_patch"], dtype=torch.float32).pin_memory()
+
+    def block_ops(w):
+        h = v["hidden"]
+        return [
+            ("rms_norm", lambda: gpu.op("rms_norm_f32", act["norm"], act["hidden"], w["norm1"], rows, h, 1e-5), 0.0),
+            ("qkv_proj", lambda: gpu.op("linear_f32", act["qkv"], act["norm"], w["qkv_w"], w["qkv_b"], rows, h, inner * 3),
+             2.0 * rows * h * inner * 3),
+            ("qkv_norm_rope", lambda: gpu.op("video_qkv_rope_f32", act["query"], act["key"], act["value"], act["qkv"],
+                                             rope_cos, rope_sin, rows, v["heads"], v["head_dim"], v["rope_half"], 1e-5), 0.0),
+            ("attention", lambda: gpu.op("sdpa_f32", act["heads"], act["query"], act["key"], act["value"], rows,
+                                         v["heads"], v["head_dim"], 0.125), 4.0 * rows * rows * inner),
+            ("out_proj", lambda: gpu.op("linear_f32", act["branch"], act["heads"], w["out_w"], w["out_b"], rows, inner, h),
+             2.0 * rows * inner * h),
+            ("scale_add", lambda: gpu.op("scale_add_f32", act["hidden"], act["hidden"], act["branch"], w["scale1"], rows, h), 0.0),
+            ("rms_norm", lambda: gpu.op("rms_norm_f32", act["norm"], act["hidden"], w["norm2"], rows, h, 1e-5), 0.0),
+            ("mlp_w1", lambda: gpu.op("linear_f32", act["ff1"], act["norm"], w["w1"], w["w1_b"], rows, h, v["ffn"] * 2),
+             2.0 * rows * h * v["ffn"] * 2),
+            ("swiglu", lambda: gpu.op("swiglu_f32", act["activated"], act["ff1"], rows, v["ffn"]), 0.0),
+            ("mlp_w2", lambda: gpu.op("linear_f32", act["branch"], act["activated"], w["w2"], w["w2_b"], rows, v["ffn"], h),
+             2.0 * rows * v["ffn"] * h),
+            ("scale_add", lambda: gpu.op("scale_add_f32", act["hidden"], act["hidden"], act["branch"], w["scale2"], rows, h), 0.0),
+        ]
+    launches_before = None
+
+    def decode_tile():
+        h = v["hidden"]
+        gpu.begin()
+        gpu.op("linear_f32", act["post"], act["latent"], post_w, post_b, patches, v["latent"], v["latent"])
+        gpu.op("linear_f32", act["patch_hidden"], act["post"], embed_w, embed_b, patches, v["latent"], h)
+        gpu.op("copy_f32", act["hidden"], 0, act["patch_hidden"], 0, patches * h)
+        gpu.op("copy_f32", act["hidden"], patches * h, registers, 0, v["registers"] * h)
+        gpu.op("copy_f32", act["hidden"], (patches + v["registers"]) * h, zero, 0, h)
+        for w in blocks:
+            for _, op, _ in block_ops(w):
+                op()
+        gpu.op("layer_norm_f32", act["norm"], act["hidden"], norm_out_w, norm_out_b, rows, h, 1e-5)
+        gpu.op("linear_f32", act["projected"], act["norm"], proj_w, proj_b, rows, h, v["output_patch"])
+        gpu.submit()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(args.warmup):
+        decode_tile()
+    sync()
+    stats0 = gpu.stats()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        decode_tile()
+    stop.record()
+    sync()
+    stats1 = gpu.stats()
+    ms = start.elapsed_time(stop) / args.steps
+    # end to end: host latent rows in, projected pixels out, every step
+    latent_view, out_view = mem.torch_of(act["latent"]), mem.torch_of(act["projected"])
+    sync()
+    start.record()
+    for _ in range(args.steps):
+        latent_view.copy_(host_latent, non_blocking=True)
+        decode_tile()
+        host_out.copy_(out_view, non_blocking=True)
+    stop.record()
+    sync()
+    e2e_ms = start.elapsed_time(stop) / args.steps
+    clocks = sampler.stop()
+    if world > 1:
+        both = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(both, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = (float(x) for x in both)
+    launches = sum(getattr(stats1, f) - getattr(stats0, f) for f in
+                   ("direct_dispatches", "mps_linear_dispatches", "mps_sdpa_dispatches")) // args.steps
+    kernels = {}
+    for name, op, flops in block_ops(blocks[0]):
+        if name in kernels:
+            continue
+        t, tf = time_kernel(torch, gpu, op, flops, 10)
+        kernels[name] = {"ms": t}
+        if flops:
+            kernels[name].update(tflops=tf, frac_of_burst_peak=tf / peaks["bf16_tflops"])
+    if rank == 0 and world == 1 and REF_CUDA.exists() and not args.no_reference_cuda:
+        for name, t in vae_reference_cuda_ops(pkg, rows).items():
+            kernels[name]["reference_cuda_ms"] = t
+        kernels["block"] = {"ms": sum(k["ms"] * (2 if n in ("rms_norm", "scale_add") else 1) for n, k in kernels.items()),
+                            "reference_cuda_ms": sum(k["reference_cuda_ms"] * (2 if n in ("rms_norm", "scale_add") else 1)
+                                                     for n, k in kernels.items())}
+    flops = sum(f for _, _, f in block_ops(blocks[0])) * v["layers"] + 2.0 * rows * v["hidden"] * v["output_patch"]
+    top = kernels["mlp_w1"]
+    line = {
+        "metric": "vae_tile_decode_ms", "value": ms, "unit": "ms/tile", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 tensors; projections on the FP16 tensor cores (row-scaled, F32 accumulate), attention in BF16",
+        "data": "synthetic",
+        "config": {"workload": "vae_tile: one 256-pixel tile of seven latent frames through the video-VAE decoder: "
+                               f"1,797 rows, hidden 2048, 32 heads x 64, FFN 8192, {v['layers']} blocks, "
+                               f"{v['layers'] * 0.268:.1f} GB of F32 weights resident",
+                   "rows": rows, "blocks": v["layers"], "parallelism": "single" if world == 1 else f"{world} replicas",
+                   "l2": "a block's weights (268 MB) exceed the 126 MB L2 between reuses"},
+        "tflops_per_gpu": flops / (ms * 1e-3) / 1e12,
+        "e2e": {"value": e2e_ms, "unit": "ms/tile", "h2d_bytes_per_step": host_latent.numel() * 4,
+                "d2h_bytes_per_step": host_out.numel() * 4},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "kernel": "h3b_gemm_pair<store f32> (MLP input projection 2048 -> 2 x 8192: the "
+                     "launch with the largest share of a block)", "achieved": top["tflops"], "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": top["tflops"] / peaks["bf16_tflops"],
+                     "peak_source": f"{peaks['source']} burst (16-bit dense)", "ms_per_launch": top["ms"],
+                     "flops_per_launch": 2.0 * rows * v["hidden"] * v["ffn"] * 2, "traffic": None,
+                     "note": "ms includes the conversion of the activation rows to FP16 (its own small launch)"},
+        "kernels": kernels, "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_ms, desc, threads, _ = vae_cpu_sample()
+        line["cpu_baseline"] = {"value": cpu_ms, "unit": "ms/tile", "cores": threads, "kind": "port", "sample": desc}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    gpu.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def vae_reference_cuda_ops(pkg, rows):
+    """The decoder block's ops through the reference's own CUDA backend (TF32 cuBLASLt projections,
+    BF16 flash attention, its row kernels) on this GPU: name -> ms."""
+    import torch
+    v = VAE
+    inner, h = v["heads"] * v["head_dim"], v["hidden"]
+    gpu = pkg.Gpu(0, lib_path=REF_CUDA)
+    rng = np.random.default_rng(0)
+
+    def T(n, std=1.0):
+        return gpu.f32(rng.standard_normal(n, dtype=np.float32) * np.float32(std))
+    x, norm, qkv = T(rows * h), T(rows * h), T(rows * inner * 3)
+    q, k, val, heads = T(rows * inner), T(rows * inner), T(rows * inner), T(rows * inner)
+    branch, ff1, act = T(rows * h), T(rows * v["ffn"] * 2), T(rows * v["ffn"])
+    cos, sin = T(rows * v["rope_half"]), T(rows * v["rope_half"])
+    w = dict(norm=T(h), qkv_w=T(inner * 3 * h, 0.02), qkv_b=T(inner * 3, 0.02), out_w=T(h * inner, 0.02), out_b=T(h, 0.02),
+             scale=T(h, 0.1), w1=T(v["ffn"] * 2 * h, 0.02), w1_b=T(v["ffn"] * 2, 0.02), w2=T(h * v["ffn"], 0.01), w2_b=T(h, 0.02))
+    ops = {
+        "rms_norm": lambda: gpu.op("rms_norm_f32", norm, x, w["norm"], rows, h, 1e-5),
+        "qkv_proj": lambda: gpu.op("linear_f32", qkv, norm, w["qkv_w"], w["qkv_b"], rows, h, inner * 3),
+        "qkv_norm_rope": lambda: gpu.op("video_qkv_rope_f32", q, k, val, qkv, cos, sin, rows, v["heads"], v["head_dim"],
+                                        v["rope_half"], 1e-5),
+        "attention": lambda: gpu.op("sdpa_f32", heads, q, k, val, rows, v["heads"], v["head_dim"], 0.125),
+        "out_proj": lambda: gpu.op("linear_f32", branch, heads, w["out_w"], w["out_b"], rows, inner, h),
+        "scale_add": lambda: gpu.op("scale_add_f32", x, x, branch, w["scale"], rows, h),
+        "mlp_w1": lambda: gpu.op("linear_f32", ff1, norm, w["w1"], w["w1_b"], rows, h, v["ffn"] * 2),
+        "swiglu": lambda: gpu.op("swiglu_f32", act, ff1, rows, v["ffn"]),
+        "mlp_w2": lambda: gpu.op("linear_f32", branch, act, w["w2"], w["w2_b"], rows, v["ffn"], h),
+    }
+    out = {name: time_kernel(torch, gpu, fn, 0.0, 10)[0] for name, fn in ops.items()}
+    gpu.close()
+    return out
+
+
 def run_sdpa_only(pkg, rows, heads):
     """Three launches of the dense attention kernel on its own: a case small enough for a
     multi-section profiler capture (rows x heads x 128 x 3 inputs; 6400,12 holds 118 MB)."""
@@ -983,6 +1254,12 @@ def main():
     pkg = entry.load_package()
     if args.sdpa_only:
         run_sdpa_only(pkg, *map(int, args.sdpa_only.split(",")))
+        return
+    if args.workload == "vae_tile":
+        if args.impl == "reference":
+            run_vae_reference_arm(args)
+        else:
+            run_vae_arm(args)
         return
     text_rows, video_rows, _ = WORKLOADS[args.workload]
     shape = pkg.DitShape(blocks=args.blocks)

@@ -161,6 +161,13 @@ void h3b_written(h3_gpu_tensor *tensor) {
     tensor->half_k = 0;
 }
 
+extern "C" int h3x_tensor_keep_half_rows(h3_gpu_tensor *tensor, int on) {
+    if (!tensor || tensor->dtype != H3_GPU_F32) return 0;
+    h3b_written(tensor);
+    tensor->keeps_half = on != 0;
+    return 1;
+}
+
 void *h3b_workspace(h3_gpu *gpu, size_t bytes) {
     if (!bytes) bytes = 1;
     if (gpu->workspace && bytes <= gpu->workspace_bytes) return gpu->workspace;

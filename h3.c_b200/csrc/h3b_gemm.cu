@@ -1065,7 +1065,7 @@ int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tens
     const size_t x_bytes = rounded(size_t(rows) * k * sizeof(uint16_t)), x_scale_bytes = rounded(size_t(rows) * sizeof(float));
     const size_t w_bytes = rounded(size_t(n) * k * sizeof(uint16_t)), w_scale_bytes = rounded(size_t(n) * sizeof(float));
     /* the weight's FP16 rows: kept with a tensor that was created with contents, else scratch */
-    h3_gpu_tensor *keeper = weight->keeps_half && !weight->external && weight->elements == size_t(n) * k
+    h3_gpu_tensor *keeper = weight->keeps_half && weight->elements == size_t(n) * k
                                 ? const_cast<h3_gpu_tensor *>(weight) : nullptr;
     uint8_t *scratch = static_cast<uint8_t *>(
         h3b_workspace(gpu, x_bytes + x_scale_bytes + (keeper ? 0 : w_bytes + w_scale_bytes)));

@@ -434,6 +434,12 @@ int h3x_cfg_combine_bf16(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_tensor *c
  * fused = bf16(input . fc1^T) with fc1 = [gate rows | up rows] of hidden_dim each, then
  * output[r][c] = bf16(silu(fused[r][c]) * fused[r][hidden_dim + c]); output is [rows][hidden_dim].
  * Counted as one projection. */
+/* Declares that an F32 tensor serves as a projection weight (on != 0) or no longer does (0).
+ * h3_gpu_linear_f32 keeps the scaled FP16 rows of such a weight between calls instead of
+ * converting it every time; tensors made by h3_gpu_tensor_load_f32 / h3_gpu_tensor_from_f32 are
+ * declared so already. Every call of this library that writes the tensor drops the rows; after a
+ * write this library cannot see (a wrapped tensor written by its owner) call this with on again. */
+int h3x_tensor_keep_half_rows(h3_gpu_tensor *tensor, int on);
 int h3x_linear_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
                            const h3_gpu_tensor *fc1_weight, uint32_t rows, uint32_t input_dim,
                            uint32_t hidden_dim);
