@@ -358,32 +358,51 @@ __device__ __forceinline__ void tile_epilogue(const TcArgs &args, uint32_t lane_
                         }
                     }
                 } else if (EPI == H3B_EPI_STORE_F32) {
-                    /* the accumulator as it is (+ F32 bias): `out` and `bias` point to F32 */
-                    float *dst = reinterpret_cast<float *>(args.out) + size_t(row) * args.out_cols + n_blk * BN;
+                    /* the accumulator times the two scales (+ F32 bias): `out` and `bias` point to F32.
+                     * A thread holds 32 columns of ITS row; stored like that, a warp's store touches 32
+                     * rows with 16 bytes each. The 32 x 32 block goes through the warp's staging area
+                     * instead (16-byte pieces XOR-swizzled by row, conflict-free both ways) and leaves as
+                     * four whole 128-byte row segments per store instruction. */
                     const float *bias = reinterpret_cast<const float *>(args.bias);
                     const float row_scale = args.row_scale && row_ok ? args.row_scale[row] : 1.0f;
+                    const uint32_t row0 = row - lane, piece = lane & 7, sub = lane >> 3;
     #pragma unroll 1
                     for (int c = 0; c < BN / 32; c++) {
+                        const uint32_t col0 = n_blk * BN + c * 32;
+                        if (col0 >= args.out_cols) break;
                         uint32_t r[32];
                         tmem_ld32(lane_addr + c * 32, r);
                         tmem_ld_wait();
-                        const uint32_t col0 = n_blk * BN + c * 32;
     #pragma unroll
                         for (int v = 0; v < 8; v++) {
-                            if (col0 + v * 4 >= args.out_cols) break;
                             float4 value = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
                                                        __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                            if (args.col_scale) {
+                            if (args.col_scale && col0 + v * 4 < args.out_cols) {
                                 const float4 s = __ldg(reinterpret_cast<const float4 *>(args.col_scale + col0 + v * 4));
                                 value.x *= row_scale * s.x; value.y *= row_scale * s.y;
                                 value.z *= row_scale * s.z; value.w *= row_scale * s.w;
                             }
-                            if (bias) {
-                                const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + col0 + v * 4));
-                                value.x += b.x; value.y += b.y; value.z += b.z; value.w += b.w;
-                            }
-                            if (row_ok) *reinterpret_cast<float4 *>(dst + c * 32 + v * 4) = value;
+                            const uint32_t addr = stage_smem + lane * 128 + ((uint32_t(v) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(value.x),
+                                         "f"(value.y), "f"(value.z), "f"(value.w) : "memory");
                         }
+                        __syncwarp();
+                        const uint32_t col = col0 + piece * 4;
+                        float4 b = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        if (bias && col < args.out_cols) b = __ldg(reinterpret_cast<const float4 *>(bias + col));
+    #pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const uint32_t rr = sub + 4 * i;
+                            float4 value;
+                            const uint32_t addr = stage_smem + rr * 128 + ((piece ^ (rr & 7)) << 4);
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w) : "r"(addr) : "memory");
+                            value.x += b.x; value.y += b.y; value.z += b.z; value.w += b.w;
+                            if (row0 + rr < args.rows && col < args.out_cols)
+                                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(args.out) +
+                                                            size_t(row0 + rr) * args.out_cols + col) = value;
+                        }
+                        __syncwarp();
                     }
                 } else {
                     uint16_t *dst = args.out + size_t(row) * args.out_cols + n_blk * BN;
@@ -592,12 +611,15 @@ h3b_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
  * barriers of both CTAs; the epilogue warps of both CTAs arrive on the even CTA's
  * accumulator-free barrier. Every wait is bounded as in the lone-CTA kernel. */
 constexpr int PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2;          /* 32 KiB per CTA and stage */
+/* the epilogues that stage rows through shared memory give up a stage for it */
 template <int EPI>
-constexpr int pair_stages() { return EPI == H3B_EPI_QKV_ROPE ? 5 : 6; }
+constexpr bool stages_rows() { return EPI == H3B_EPI_QKV_ROPE || EPI == H3B_EPI_STORE_F32; }
+template <int EPI>
+constexpr int pair_stages() { return stages_rows<EPI>() ? 5 : 6; }
 template <int EPI>
 constexpr size_t pair_smem() {
     return size_t(pair_stages<EPI>()) * PAIR_STAGE_BYTES + 1024 + 256 +
-           (EPI == H3B_EPI_QKV_ROPE ? 4 * QKV_STAGE_BYTES : 0);
+           (stages_rows<EPI>() ? 4 * QKV_STAGE_BYTES : 0);
 }
 
 template <int EPI>
@@ -944,7 +966,7 @@ int launch_tc(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t *w,
               const TcArgs *extra = nullptr) {
     static bool configured_on[64];      /* the attribute is per device */
     static std::mutex configure_mutex;
-    constexpr size_t smem_bytes = EPI == H3B_EPI_QKV_ROPE ? TC_SMEM_QKV : TC_SMEM;
+    constexpr size_t smem_bytes = stages_rows<EPI>() ? TC_SMEM_QKV : TC_SMEM;
     std::unique_lock<std::mutex> configure_guard(configure_mutex);
     bool &configured = configured_on[gpu->device & 63];
     if (!configured) {
