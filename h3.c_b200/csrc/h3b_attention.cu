@@ -1456,9 +1456,9 @@ extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
         for (int i = 0; i < 4; i++) {
             half[i] = h3_gpu_tensor{scratch + i * padded, padded, padded * sizeof(uint16_t), H3_GPU_BF16, gpu, 1};
         }
-        h3b_f32_to_bf16_pad(gpu, h3b_ptr<float>(query), scratch, units, head_dim, AT_D);
-        h3b_f32_to_bf16_pad(gpu, h3b_ptr<float>(key), scratch + padded, units, head_dim, AT_D);
-        h3b_f32_to_bf16_pad(gpu, h3b_ptr<float>(value), scratch + 2 * padded, units, head_dim, AT_D);
+        const float *const sources[3] = {h3b_ptr<float>(query), h3b_ptr<float>(key), h3b_ptr<float>(value)};
+        uint16_t *const targets[3] = {scratch, scratch + padded, scratch + 2 * padded};
+        h3b_f32_to_bf16_pad3(gpu, sources, targets, units, head_dim, AT_D);
         if (!h3b_launched(gpu, "sdpa_f32 operands")) return 0;
         /* a block-sparse mask registered for the DiT's BF16 attention does not apply here (the
          * reference passes none on this route, h3_cuda_attention.cu:3010) */

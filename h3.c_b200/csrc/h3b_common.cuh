@@ -230,8 +230,8 @@ int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tens
 void *h3b_device_alloc(h3_gpu *gpu, size_t bytes);           /* the tensors' block cache */
 void h3b_device_release(h3_gpu *gpu, void *data, size_t bytes);
 /* conversion kernels (h3b_f32ops.cu) */
-void h3b_f32_to_bf16_pad(h3_gpu *gpu, const float *in, uint16_t *out, size_t units, uint32_t dims,
-                         uint32_t padded);
+void h3b_f32_to_bf16_pad3(h3_gpu *gpu, const float *const in[3], uint16_t *const out[3], size_t units,
+                          uint32_t dims, uint32_t padded);
 void h3b_bf16_to_f32_unpad(h3_gpu *gpu, const uint16_t *in, float *out, size_t units, uint32_t dims,
                            uint32_t padded);
 /* F32 [rows][k] -> FP16 [rows][k] scaled per row by a power of two, inverse scales to `inverse` */

@@ -216,9 +216,15 @@ h3b_video_qkv_rope_f32_kernel(const float *__restrict__ qkv, const float *__rest
     }
 }
 
-/* F32 [units][dims] -> BF16 [units][padded], zeros behind the dims (4 output values per thread) */
-__global__ void h3b_f32_to_bf16_pad_kernel(const float *__restrict__ in, uint16_t *__restrict__ out, size_t units,
-                                           uint32_t dims, uint32_t padded) {
+/* F32 [units][dims] -> BF16 [units][padded], zeros behind the dims (4 output values per thread);
+ * blockIdx.y picks one of up to three tensors of the same shape (q, k, v in one launch) */
+struct PadCast {
+    const float *in[3];
+    uint16_t *out[3];
+};
+__global__ void h3b_f32_to_bf16_pad_kernel(PadCast tensors, size_t units, uint32_t dims, uint32_t padded) {
+    const float *__restrict__ in = tensors.in[blockIdx.y];
+    uint16_t *__restrict__ out = tensors.out[blockIdx.y];
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint32_t groups = padded / 4;
     if (i >= units * groups) return;
@@ -282,11 +288,16 @@ h3b_scale_rows_f16_kernel(const float *__restrict__ in, uint16_t *__restrict__ o
 
 }  // namespace
 
-void h3b_f32_to_bf16_pad(h3_gpu *gpu, const float *in, uint16_t *out, size_t units, uint32_t dims,
-                         uint32_t padded) {
+void h3b_f32_to_bf16_pad3(h3_gpu *gpu, const float *const in[3], uint16_t *const out[3], size_t units,
+                          uint32_t dims, uint32_t padded) {
     const size_t items = units * (padded / 4);
-    if (items)
-        h3b_f32_to_bf16_pad_kernel<<<blocks_for(items, 256), 256, 0, gpu->stream>>>(in, out, units, dims, padded);
+    if (!items) return;
+    PadCast tensors;
+    for (int i = 0; i < 3; i++) {
+        tensors.in[i] = in[i];
+        tensors.out[i] = out[i];
+    }
+    h3b_f32_to_bf16_pad_kernel<<<dim3(blocks_for(items, 256), 3), 256, 0, gpu->stream>>>(tensors, units, dims, padded);
 }
 
 void h3b_bf16_to_f32_unpad(h3_gpu *gpu, const uint16_t *in, float *out, size_t units, uint32_t dims,
