@@ -25,8 +25,9 @@ struct h3_gpu_tensor {
     int external;  /* wraps caller-owned memory: never freed or cached */
     /* F32 tensors created with contents (file loads, from_f32) may serve as projection weights:
      * h3_gpu_linear_f32 keeps their rows as scaled FP16 + one F32 scale per row here (see
-     * h3b_gemm_f32_half). Dropped by h3b_written() whenever this library writes the tensor, and
-     * with the tensor. */
+     * h3b_gemm_f32_half). The norms, whose result usually feeds a projection, leave the same form
+     * beside their output. Dropped by h3b_written() whenever
+     * this library writes the tensor, and with the tensor. */
     int keeps_half = 0;
     void *half_rows = nullptr;      /* [rows][k] FP16, then rows F32 inverse scales */
     size_t half_bytes = 0;
@@ -225,8 +226,11 @@ bool h3b_tensor_map_available();
  * two inverse scales (exact) and adds the bias. The weight's FP16 rows are kept with the weight
  * tensor when it was created with contents. Returns -1 when the shape cannot take this route
  * (caller runs the exact F32 kernel). */
-int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tensor *weight,
+int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
                       const float *bias, uint32_t rows, uint32_t k, uint32_t n);
+/* scaled FP16 rows beside an activation tensor, written by the op that produces it (h3b_f32ops.cu) */
+uint16_t *h3b_half_rows_attach(h3_gpu *gpu, h3_gpu_tensor *t, size_t rows, uint32_t k, float **inverse);
+
 void *h3b_device_alloc(h3_gpu *gpu, size_t bytes);           /* the tensors' block cache */
 void h3b_device_release(h3_gpu *gpu, void *data, size_t bytes);
 /* conversion kernels (h3b_f32ops.cu) */

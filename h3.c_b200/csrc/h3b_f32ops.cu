@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <initializer_list>
 
 namespace {
@@ -223,8 +224,9 @@ struct PadCast {
     uint16_t *out[3];
 };
 __global__ void h3b_f32_to_bf16_pad_kernel(PadCast tensors, size_t units, uint32_t dims, uint32_t padded) {
-    const float *__restrict__ in = tensors.in[blockIdx.y];
-    uint16_t *__restrict__ out = tensors.out[blockIdx.y];
+    /* picked with selects: indexing the parameter arrays with blockIdx.y would move them to local memory */
+    const float *__restrict__ in = blockIdx.y == 0 ? tensors.in[0] : blockIdx.y == 1 ? tensors.in[1] : tensors.in[2];
+    uint16_t *__restrict__ out = blockIdx.y == 0 ? tensors.out[0] : blockIdx.y == 1 ? tensors.out[1] : tensors.out[2];
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint32_t groups = padded / 4;
     if (i >= units * groups) return;
@@ -286,7 +288,140 @@ h3b_scale_rows_f16_kernel(const float *__restrict__ in, uint16_t *__restrict__ o
     }
 }
 
+/* ---- producers that also leave their rows as scaled FP16 --------------------------------------
+ * A projection (h3_gpu_linear_f32 on the tensor cores) needs its input rows as FP16 scaled per row
+ * by a power of two. The norms, whose output feeds a projection in the decoder, hold a whole row
+ * in registers anyway, so they write that form beside the F32 result and spare the projection its
+ * conversion launch (QKV projection 57 -> 47 us at 1,797 rows, the norm itself +0.5 us). The same
+ * was tried for SwiGLU and for the attention result and dropped: one CTA per row with a reduction
+ * in the middle cost those two as much as the conversion launch saved. PER = 16-byte vectors per
+ * thread (row width <= 1024 * PER). */
+__device__ __forceinline__ float cta_max(float value, float *scratch) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) value = fmaxf(value, __shfl_xor_sync(0xffffffffu, value, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = value;
+    __syncthreads();
+    float largest = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; w++) largest = fmaxf(largest, scratch[w]);
+    return largest;
+}
+
+/* power-of-two scale that brings `largest` into [2^13, 2^14), and its inverse */
+__device__ __forceinline__ float half_row_scale(float largest, float *inverse) {
+    const int field = int((__float_as_uint(largest) >> 23) & 0xffu);
+    int scale_field = 127 + 13 - (field - 127);
+    if (field == 0 || field == 255) scale_field = 127;      /* zero / subnormal / inf / nan rows: scale 1 */
+    scale_field = min(max(scale_field, 1), 253);
+    *inverse = __uint_as_float(uint32_t(254 - scale_field) << 23);
+    return __uint_as_float(uint32_t(scale_field) << 23);
+}
+
+__device__ __forceinline__ uint2 to_half4(float4 v, float scale) {
+    const __half2 lo = __floats2half2_rn(v.x * scale, v.y * scale), hi = __floats2half2_rn(v.z * scale, v.w * scale);
+    return make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+}
+
+template <int PER>
+__device__ __forceinline__ void store_half_row(const float4 (&y)[PER], uint32_t vectors, uint16_t *half_row,
+                                               float *inverse, float *scratch) {
+    float largest = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+        if (threadIdx.x + j * kRowThreads < vectors)
+            largest = fmaxf(fmaxf(largest, fmaxf(fabsf(y[j].x), fabsf(y[j].y))), fmaxf(fabsf(y[j].z), fabsf(y[j].w)));
+    float undo;
+    const float scale = half_row_scale(cta_max(largest, scratch), &undo);
+    if (threadIdx.x == 0) *inverse = undo;
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+        if (threadIdx.x + j * kRowThreads < vectors)
+            reinterpret_cast<uint2 *>(half_row)[threadIdx.x + j * kRowThreads] = to_half4(y[j], scale);
+}
+
+/* RMSNorm (LAYER = false) or LayerNorm with the row held in registers: one read of x, F32 result,
+ * and, when half_rows is given, the scaled FP16 row */
+template <bool LAYER, int PER>
+__global__ void __launch_bounds__(kRowThreads)
+h3b_norm_f32_rows_kernel(const float *__restrict__ input, const float *__restrict__ weight,
+                         const float *__restrict__ bias, float *__restrict__ output, uint16_t *__restrict__ half_rows,
+                         float *__restrict__ inverse, uint32_t width, float epsilon) {
+    __shared__ float scratch[kRowThreads / 32];
+    const uint32_t vectors = width / 4;
+    const float4 *x = reinterpret_cast<const float4 *>(input + size_t(blockIdx.x) * width);
+    float4 v[PER];
+    float local = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const uint32_t i = threadIdx.x + j * kRowThreads;
+        v[j] = i < vectors ? x[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (LAYER) {
+            local += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        } else {
+            local = fmaf(v[j].x, v[j].x, local); local = fmaf(v[j].y, v[j].y, local);
+            local = fmaf(v[j].z, v[j].z, local); local = fmaf(v[j].w, v[j].w, local);
+        }
+    }
+    float mean = 0.0f;
+    if (LAYER) {
+        mean = cta_sum(local, scratch) / float(width);
+        local = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (threadIdx.x + j * kRowThreads < vectors) {
+                const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+                local = fmaf(a, a, local); local = fmaf(b, b, local);
+                local = fmaf(c, c, local); local = fmaf(d, d, local);
+            }
+    }
+    const float scale = 1.0f / sqrtf(cta_sum(local, scratch) / float(width) + epsilon);
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const uint32_t i = threadIdx.x + j * kRowThreads;
+        if (i < vectors) {
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(weight) + i);
+            if (LAYER) {
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(bias) + i);
+                v[j] = make_float4((v[j].x - mean) * scale * w.x + b.x, (v[j].y - mean) * scale * w.y + b.y,
+                                   (v[j].z - mean) * scale * w.z + b.z, (v[j].w - mean) * scale * w.w + b.w);
+            } else {
+                v[j] = make_float4(v[j].x * scale * w.x, v[j].y * scale * w.y, v[j].z * scale * w.z, v[j].w * scale * w.w);
+            }
+            reinterpret_cast<float4 *>(output + size_t(blockIdx.x) * width)[i] = v[j];
+        }
+    }
+    if (half_rows) store_half_row<PER>(v, vectors, half_rows + size_t(blockIdx.x) * width, inverse + blockIdx.x, scratch);
+}
+
+/* launches KERNEL<PER> with the smallest PER in {1, 2, 4, 8} that covers `width` */
+#define H3B_FOR_ROW_WIDTH(width, CALL)                \
+    do {                                              \
+        if ((width) <= 1024) { constexpr int PER = 1; CALL; }        \
+        else if ((width) <= 2048) { constexpr int PER = 2; CALL; }   \
+        else if ((width) <= 4096) { constexpr int PER = 4; CALL; }   \
+        else { constexpr int PER = 8; CALL; }                        \
+    } while (0)
+
 }  // namespace
+
+/* Room for the scaled FP16 form of `rows` rows of width k beside tensor t (dropped like a weight's
+ * rows by h3b_written): null when the rows cannot feed the tensor-core projection route, when t
+ * wraps caller-owned memory (writes by its owner would go unseen), or when H3B_NO_HALF_ROWS=1. */
+uint16_t *h3b_half_rows_attach(h3_gpu *gpu, h3_gpu_tensor *t, size_t rows, uint32_t k, float **inverse) {
+    static const bool off = [] { const char *v = getenv("H3B_NO_HALF_ROWS"); return v && *v && strcmp(v, "0") != 0; }();
+    if (off || t->external || k < 1024 || k % 8 != 0 || k > 8192 || t->elements != rows * k ||
+        !h3b_aligned16(t->data))
+        return nullptr;
+    const size_t row_bytes = (rows * k * sizeof(uint16_t) + 255) & ~size_t(255);
+    const size_t bytes = row_bytes + ((rows * sizeof(float) + 255) & ~size_t(255));
+    t->half_rows = h3b_device_alloc(gpu, bytes);
+    if (!t->half_rows) return nullptr;
+    t->half_bytes = bytes;
+    t->half_k = k;
+    *inverse = reinterpret_cast<float *>(static_cast<uint8_t *>(t->half_rows) + row_bytes);
+    return static_cast<uint16_t *>(t->half_rows);
+}
 
 void h3b_f32_to_bf16_pad3(h3_gpu *gpu, const float *const in[3], uint16_t *const out[3], size_t units,
                           uint32_t dims, uint32_t padded) {
@@ -326,7 +461,12 @@ extern "C" int h3_gpu_rms_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_
     if (count) {
         const float *x = h3b_ptr<float>(input), *w = h3b_ptr<float>(weight);
         float *y = h3b_ptr<float>(output);
-        if (width % 4 == 0 && aligned16({x, w, y}))
+        if (width % 4 == 0 && width <= 8192 && aligned16({x, w, y})) {
+            float *inverse = nullptr;
+            uint16_t *half_rows = h3b_half_rows_attach(gpu, output, rows, width, &inverse);
+            H3B_FOR_ROW_WIDTH(width, (h3b_norm_f32_rows_kernel<false, PER><<<rows, kRowThreads, 0, gpu->stream>>>(
+                                         x, w, nullptr, y, half_rows, inverse, width, epsilon)));
+        } else if (width % 4 == 0 && aligned16({x, w, y}))
             h3b_rms_norm_f32_kernel<true><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, y, width, epsilon);
         else
             h3b_rms_norm_f32_kernel<false><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, y, width, epsilon);
@@ -347,7 +487,12 @@ extern "C" int h3_gpu_layer_norm_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h
     if (count) {
         const float *x = h3b_ptr<float>(input), *w = h3b_ptr<float>(weight), *b = h3b_ptr<float>(bias);
         float *y = h3b_ptr<float>(output);
-        if (width % 4 == 0 && aligned16({x, w, b, y}))
+        if (width % 4 == 0 && width <= 8192 && aligned16({x, w, b, y})) {
+            float *inverse = nullptr;
+            uint16_t *half_rows = h3b_half_rows_attach(gpu, output, rows, width, &inverse);
+            H3B_FOR_ROW_WIDTH(width, (h3b_norm_f32_rows_kernel<true, PER><<<rows, kRowThreads, 0, gpu->stream>>>(
+                                         x, w, b, y, half_rows, inverse, width, epsilon)));
+        } else if (width % 4 == 0 && aligned16({x, w, b, y}))
             h3b_layer_norm_f32_kernel<true><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, b, y, width, epsilon);
         else
             h3b_layer_norm_f32_kernel<false><<<rows, kRowThreads, 0, gpu->stream>>>(x, w, b, y, width, epsilon);

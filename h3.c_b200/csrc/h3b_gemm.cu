@@ -1074,8 +1074,9 @@ int h3b_gemm_bf16(h3_gpu *gpu, uint16_t *out, const uint16_t *x, const uint16_t 
     return h3b_launched(gpu, what, H3B_LINEAR);
 }
 
-int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tensor *weight,
+int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
                       const float *bias, uint32_t rows, uint32_t k, uint32_t n) {
+    const float *x = h3b_ptr<float>(input);
     /* the reference sends an F32 projection to the tensor cores from a reduction length of
      * 1,024 on (h3_cuda_gemm.cu:246-251); shorter ones stay exact */
     const float *w = h3b_ptr<float>(weight);
@@ -1089,11 +1090,14 @@ int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tens
     /* the weight's FP16 rows: kept with a tensor that was created with contents, else scratch */
     h3_gpu_tensor *keeper = weight->keeps_half && weight->elements == size_t(n) * k
                                 ? const_cast<h3_gpu_tensor *>(weight) : nullptr;
-    uint8_t *scratch = static_cast<uint8_t *>(
-        h3b_workspace(gpu, x_bytes + x_scale_bytes + (keeper ? 0 : w_bytes + w_scale_bytes)));
+    /* the input's FP16 rows: left beside it by the op that produced it, else converted here */
+    const bool ready = input->half_rows && input->half_k == k && input->elements == size_t(rows) * k;
+    const size_t x_room = ready ? 0 : x_bytes + x_scale_bytes;
+    uint8_t *scratch = static_cast<uint8_t *>(h3b_workspace(gpu, x_room + (keeper ? 0 : w_bytes + w_scale_bytes)));
     if (!scratch) return h3b_fail(gpu, "linear_f32: cannot allocate the FP16 operands");
-    uint16_t *x16 = reinterpret_cast<uint16_t *>(scratch);
-    float *x_scale = reinterpret_cast<float *>(scratch + x_bytes);
+    uint16_t *x16 = ready ? static_cast<uint16_t *>(input->half_rows) : reinterpret_cast<uint16_t *>(scratch);
+    float *x_scale = ready ? reinterpret_cast<float *>(static_cast<uint8_t *>(input->half_rows) + x_bytes)
+                           : reinterpret_cast<float *>(scratch + x_bytes);
     uint16_t *w16;
     float *w_scale;
     if (keeper) {
@@ -1109,11 +1113,11 @@ int h3b_gemm_f32_half(h3_gpu *gpu, float *out, const float *x, const h3_gpu_tens
         w16 = static_cast<uint16_t *>(keeper->half_rows);
         w_scale = reinterpret_cast<float *>(static_cast<uint8_t *>(keeper->half_rows) + w_bytes);
     } else {
-        w16 = reinterpret_cast<uint16_t *>(scratch + x_bytes + x_scale_bytes);
-        w_scale = reinterpret_cast<float *>(scratch + x_bytes + x_scale_bytes + w_bytes);
+        w16 = reinterpret_cast<uint16_t *>(scratch + x_room);
+        w_scale = reinterpret_cast<float *>(scratch + x_room + w_bytes);
         h3b_scale_rows_f16(gpu, w, w16, w_scale, n, k);
     }
-    h3b_scale_rows_f16(gpu, x, x16, x_scale, rows, k);
+    if (!ready) h3b_scale_rows_f16(gpu, x, x16, x_scale, rows, k);
     if (cudaGetLastError() != cudaSuccess) return h3b_fail(gpu, "linear_f32: operand conversion failed");
     TcArgs extra = {};
     extra.row_scale = x_scale;
@@ -1199,7 +1203,7 @@ extern "C" int h3_gpu_linear_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gp
         !h3b_need_command(gpu))
         return 0;
     h3b_written(output);
-    const int served = h3b_gemm_f32_half(gpu, h3b_ptr<float>(output), h3b_ptr<float>(input), weight,
+    const int served = h3b_gemm_f32_half(gpu, h3b_ptr<float>(output), input, weight,
                                          bias ? h3b_ptr<float>(bias) : nullptr, rows, input_dim, output_dim);
     if (served == 0) return 0;
     if (served < 0 && rows && output_dim)
