@@ -797,21 +797,26 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
  * its tiles (128 KiB per tile step) but pays the serial chain. All waits are mbarrier waits with
  * the context's budget (no named barriers: a group that gives up can never leave the other one
  * blocked). Dense attention only; the block-sparse mask keeps the two-tile kernel. */
-constexpr int A2_QT = 128, A2_KV = 128, A2_D = 128;
+constexpr int A2_QT = 128, A2_KV = 128;
+constexpr int A2_BOX_BYTES = A2_KV * 64 * 2;                /* a TMA box: 128 rows x 64 dims = 16 KiB */
 constexpr int A2_STAGES = 3, A2_S_BUFFERS = 3;
 constexpr int A2_THREADS = 64 + 32 * 8;                    /* producer, MMA, 2 groups x 4 softmax warps */
-constexpr int A2_TILE_BYTES = A2_KV * A2_D * 2;             /* 32 KiB: Q tile, K stage, V stage */
+/* Q tile, K stage, V stage of head_dim D (128: two boxes, 64: one) */
+template <int D>
+constexpr int a2_tile_bytes() { return A2_KV * D * 2; }
 constexpr int A2_BAR_BYTES = 512;
 constexpr int A2_STATE_BYTES = 5 * A2_QT * 4;   /* per row: reference maximum; (sum, its reference) per group */
-constexpr size_t A2_SMEM = size_t(1 + 2 * A2_STAGES) * A2_TILE_BYTES + A2_BAR_BYTES +
-                           A2_STATE_BYTES;
-static_assert(A2_SMEM <= 232448, "the step-alternating attention kernel needs at most 227 KiB of shared memory");
+template <int D>
+constexpr size_t a2_smem() { return size_t(1 + 2 * A2_STAGES) * a2_tile_bytes<D>() + A2_BAR_BYTES + A2_STATE_BYTES; }
+static_assert(a2_smem<128>() <= 232448, "the step-alternating attention kernel needs at most 227 KiB of shared memory");
 constexpr uint32_t A2_COL_S = 0, A2_COL_O = A2_S_BUFFERS * A2_KV;
 
-template <bool PUSH>
+template <bool PUSH, int D>
 __global__ void __launch_bounds__(A2_THREADS, 1)
 h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
              const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
+    static_assert(D == 64 || D == 128, "head_dim 64 or 128");
+    constexpr int A2_D = D, A2_TILE_BYTES = a2_tile_bytes<D>();
     extern __shared__ __align__(1024) uint8_t at_smem[];
     const uint32_t base = smem_u32(at_smem);
     const uint32_t q_smem = base;
@@ -874,7 +879,7 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         if (lane == 0) {
             auto load = [&](uint32_t smem, const CUtensorMap *map, uint32_t bar, uint32_t row) {
                 tma_load_3d(smem, map, bar, 0, int(head), int(row));
-                tma_load_3d(smem + A2_TILE_BYTES / 2, map, bar, 64, int(head), int(row));
+                if (D == 128) tma_load_3d(smem + A2_BOX_BYTES, map, bar, 64, int(head), int(row));
             };
             const uint32_t first = n_steps < 3 ? n_steps : 3;
             mbar_expect_tx(q_full, (1 + first) * A2_TILE_BYTES);
@@ -902,10 +907,11 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         const uint32_t leader = lane == 0;
         constexpr uint32_t idesc_qk = instruction_desc(A2_QT, A2_KV);
         constexpr uint32_t idesc_pv = instruction_desc(A2_QT, A2_D) | (1u << 16); /* B N-major */
-        constexpr uint32_t HALF = (A2_TILE_BYTES / 2) >> 4, STAGE = A2_TILE_BYTES >> 4;
+        constexpr uint32_t HALF = A2_BOX_BYTES >> 4, STAGE = A2_TILE_BYTES >> 4;
+        constexpr int QK_MMAS = A2_D / 16;       /* 16 dims per instruction */
         const uint32_t q_lo0 = desc_lo_kmajor(q_smem);
         const uint32_t k_lo0 = desc_lo_kmajor(k_smem);
-        const uint32_t v_lo0 = desc_lo_nmajor(v_smem, A2_TILE_BYTES / 2);
+        const uint32_t v_lo0 = desc_lo_nmajor(v_smem, A2_BOX_BYTES);
         const uint32_t tmem_s0 = tmem_base + A2_COL_S, tmem_o = tmem_base + A2_COL_O;
         /* scores of a step into S[buffer] from K stage `stage` (both step % 3) */
         auto issue_qk = [&](uint32_t buffer) {
@@ -951,7 +957,7 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             if (ahead) {
                 umma_ss<false>(d, q_lo0, k_lo, idesc_qk, leader);
 #pragma unroll
-                for (int kk = 1; kk < 6; kk++)
+                for (int kk = 1; kk < QK_MMAS - 2; kk++)
                     umma_ss<true>(d, q_lo0 + (kk >> 2) * HALF + 2 * (kk & 3), k_lo + (kk >> 2) * HALF + 2 * (kk & 3),
                                   idesc_qk, leader);
             }
@@ -959,7 +965,7 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             ready = mbar_test(go + 8 * n_buffer, n_round);
             if (ahead) {
 #pragma unroll
-                for (int kk = 6; kk < 8; kk++)
+                for (int kk = QK_MMAS - 2; kk < QK_MMAS; kk++)
                     umma_ss<true>(d, q_lo0 + (kk >> 2) * HALF + 2 * (kk & 3), k_lo + (kk >> 2) * HALF + 2 * (kk & 3),
                                   idesc_qk, leader);
                 umma_commit_if(s_full + 8 * buffer, leader);
@@ -1041,7 +1047,7 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
                 tc_fence_after();
                 const float alpha = raise ? fast_exp2(row_ref - m_step) : 1.0f;
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < A2_D / 32; c++) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + c * 32, o);
                     tmem_ld_wait();
@@ -1106,7 +1112,9 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         bool finished = alive && mbar_wait(sum_bar + 8 * quarter, 0, stop, budget) &&
                         mbar_wait(o_done, 0, stop, budget);
         finished = __all_sync(0xffffffffu, finished);
-        const uint32_t stage = q_smem + quarter * 8192;
+        /* output rows staged in the Q tile's shared memory: 32 rows x D dims BF16 per quarter */
+        constexpr uint32_t ROW_BYTES = A2_D * 2, CHUNKS = A2_D / 8;          /* 16-byte pieces per row */
+        const uint32_t stage = q_smem + quarter * 32 * ROW_BYTES;
         if (finished) {
             tc_fence_after();
             const float ra = group_reference[local_row], rb = group_reference[A2_QT + local_row];
@@ -1115,16 +1123,16 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             if (ra != -INFINITY) total += group_sum[local_row] * fast_exp2(ra - r);
             if (rb != -INFINITY) total += group_sum[A2_QT + local_row] * fast_exp2(rb - r);
             const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-            /* group g owns output dims [64 g, 64 g + 64) of its rows */
+            /* group g owns output dims [D/2 g, D/2 g + D/2) of its rows */
 #pragma unroll 1
-            for (uint32_t c = 0; c < 2; c++) {
+            for (uint32_t c = 0; c < A2_D / 64; c++) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + group * 64 + c * 32, o);
+                tmem_ld32(tmem_o + group * (A2_D / 2) + c * 32, o);
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t v = 0; v < 4; v++) {
-                    const uint32_t chunk = group * 8 + c * 4 + v;
-                    const uint32_t addr = stage + lane * 256 + ((chunk ^ (lane & 15)) << 4);
+                    const uint32_t chunk = group * (CHUNKS / 2) + c * 4 + v;
+                    const uint32_t addr = stage + lane * ROW_BYTES + ((chunk ^ (lane & (CHUNKS - 1))) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
                                  "r"(pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv)),
                                  "r"(pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv)),
@@ -1139,13 +1147,14 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         }
         if (finished) {
             const uint32_t row0 = q_block * A2_QT + quarter * 32;
-            const uint32_t chunk = lane & 15;
+            constexpr uint32_t ROWS_PER_STORE = 32 / CHUNKS;         /* a warp's store covers whole rows */
+            const uint32_t chunk = lane & (CHUNKS - 1);
 #pragma unroll 1
-            for (uint32_t i = 0; i < 8; i++) {
-                const uint32_t r = group * 16 + 2 * i + (lane >> 4);
+            for (uint32_t i = 0; i < 16 / ROWS_PER_STORE; i++) {
+                const uint32_t r = group * 16 + ROWS_PER_STORE * i + lane / CHUNKS;
                 const uint32_t out_row = row0 + r;
                 uint4 val;
-                const uint32_t addr = stage + r * 256 + ((chunk ^ (r & 15)) << 4);
+                const uint32_t addr = stage + r * ROW_BYTES + ((chunk ^ (r & (CHUNKS - 1))) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr) : "memory");
                 if (out_row < args.seq) {
@@ -1182,13 +1191,13 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     }
 }
 
-/* [rows][heads][128] BF16 viewed as a 3-D tensor (dim, head, row); box = 64 dims x 1 head x box_rows */
+/* [rows][heads][hd] BF16 viewed as a 3-D tensor (dim, head, row); box = 64 dims x 1 head x box_rows */
 bool make_qkv_map(CUtensorMap *map, const uint16_t *data, uint32_t rows, uint32_t heads,
-                  uint32_t box_rows) {
+                  uint32_t box_rows, uint32_t hd = 128) {
     EncodeTiled encode = encode_tiled();
     if (!encode) return false;
-    cuuint64_t dims[3] = {128, heads, rows};
-    cuuint64_t strides[2] = {128 * 2, cuuint64_t(heads) * 128 * 2};
+    cuuint64_t dims[3] = {hd, heads, rows};
+    cuuint64_t strides[2] = {cuuint64_t(hd) * 2, cuuint64_t(heads) * hd * 2};
     cuuint32_t box[3] = {64, 1, box_rows};
     cuuint32_t elem[3] = {1, 1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<uint16_t *>(data), dims,
@@ -1222,7 +1231,10 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
     const bool sparse = gpu->sparse_cta_ptr && gpu->sparse_rows == seq;
     if (sparse && !(hd == AT_D && aligned && !simt && scale > 0.0f))
         return h3b_fail(gpu, "the block-sparse mask needs head_dim 128, aligned tensors and the tensor-core kernel");
-    if (hd == AT_D && aligned && !simt && scale > 0.0f) {
+    /* head_dim 64 (the video-VAE decoder's): dense, local output, the one-tile kernel only */
+    const char *two_tiles = getenv("H3B_SDPA_TWO_TILES");
+    const bool narrow = hd == 64 && !peers && !sparse && !(two_tiles && *two_tiles && strcmp(two_tiles, "0") != 0);
+    if ((hd == AT_D || narrow) && aligned && !simt && scale > 0.0f) {
         static bool configured_on[64];      /* the attribute is per device */
         static std::mutex configure_mutex;
         std::unique_lock<std::mutex> configure_guard(configure_mutex);
@@ -1233,9 +1245,11 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
                                  h3b_sdpa_tc<true, false>, h3b_sdpa_tc<true, true>})
                 ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 int(AT_SMEM)) == cudaSuccess;
-            for (auto *kernel : {h3b_sdpa_tc2<false>, h3b_sdpa_tc2<true>})
+            for (auto *kernel : {h3b_sdpa_tc2<false, 128>, h3b_sdpa_tc2<true, 128>})
                 ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                int(A2_SMEM)) == cudaSuccess;
+                                                int(a2_smem<128>())) == cudaSuccess;
+            ok = ok && cudaFuncSetAttribute(h3b_sdpa_tc2<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            int(a2_smem<64>())) == cudaSuccess;
             if (!ok) {
                 cudaGetLastError();
                 return h3b_fail(gpu, "cannot reserve shared memory for the attention kernel");
@@ -1248,9 +1262,9 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         const char *pick = getenv("H3B_SDPA_TWO_TILES");
         const bool step_kernel = !sparse && !(pick && *pick && strcmp(pick, "0") != 0);
         CUtensorMap map_q, map_k, map_v;
-        if (!make_qkv_map(&map_q, h3b_ptr<uint16_t>(query), seq, heads, step_kernel ? A2_QT : AT_Q) ||
-            !make_qkv_map(&map_k, h3b_ptr<uint16_t>(key), seq, heads, AT_KV) ||
-            !make_qkv_map(&map_v, h3b_ptr<uint16_t>(value), seq, heads, AT_KV))
+        if (!make_qkv_map(&map_q, h3b_ptr<uint16_t>(query), seq, heads, step_kernel ? A2_QT : AT_Q, hd) ||
+            !make_qkv_map(&map_k, h3b_ptr<uint16_t>(key), seq, heads, AT_KV, hd) ||
+            !make_qkv_map(&map_v, h3b_ptr<uint16_t>(value), seq, heads, AT_KV, hd))
             return h3b_fail(gpu, "cannot encode the attention tensor maps");
         AttnArgs args = {};
         args.out = output ? h3b_ptr<uint16_t>(output) : nullptr;
@@ -1274,8 +1288,12 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         args.head_major = head_major;
         if (step_kernel) {
             dim3 grid((seq + A2_QT - 1) / A2_QT, heads);
-            auto *kernel = peers ? h3b_sdpa_tc2<true> : h3b_sdpa_tc2<false>;
-            kernel<<<grid, A2_THREADS, A2_SMEM, gpu->stream>>>(map_q, map_k, map_v, args);
+            if (narrow) {
+                h3b_sdpa_tc2<false, 64><<<grid, A2_THREADS, a2_smem<64>(), gpu->stream>>>(map_q, map_k, map_v, args);
+                return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
+            }
+            auto *kernel = peers ? h3b_sdpa_tc2<true, 128> : h3b_sdpa_tc2<false, 128>;
+            kernel<<<grid, A2_THREADS, a2_smem<128>(), gpu->stream>>>(map_q, map_k, map_v, args);
             return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
         }
         dim3 grid((seq + AT_Q - 1) / AT_Q, heads);
@@ -1429,8 +1447,7 @@ extern "C" int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *ou
 
 /* F32 attention (the video-VAE decoder's, head_dim 64). Like the reference (h3_cuda_attention.cu:
  * 2990-3013) head sizes 64 and 128 go through the BF16 tensor-core kernel: q, k and v are rounded
- * to BF16 into scratch and the result is widened again; head_dim 64 is padded with zeros to the
- * kernel's 128 (zero dims add nothing to a score, and the output's extra dims are dropped).
+ * to BF16 into scratch (one launch) and the result is widened again.
  * Other head sizes, and H3B_SDPA_F32_EXACT=1 (the reference's H3_CUDA_SDPA_F32_EXACT), take the
  * F32 SIMT kernel. */
 extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
@@ -1449,7 +1466,12 @@ extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
                          h3b_aligned16(value->data) && h3b_aligned16(output->data);
     if ((head_dim == 64 || head_dim == 128) && aligned && scale > 0.0f && h3b_tensor_map_available() &&
         !(exact && *exact && strcmp(exact, "0") != 0) && !getenv("H3B_SDPA_SIMT")) {
-        const size_t units = size_t(sequence) * heads, padded = units * AT_D;
+        /* head_dim 64 runs as it is on the one-tile kernel; where that kernel is switched off
+         * (H3B_SDPA_TWO_TILES=1) it is padded with zeros to 128: zero dims add nothing to a score,
+         * and the output's extra dims are dropped */
+        const char *two_tiles = getenv("H3B_SDPA_TWO_TILES");
+        const uint32_t run_dim = head_dim == 64 && !(two_tiles && *two_tiles && strcmp(two_tiles, "0") != 0) ? 64 : AT_D;
+        const size_t units = size_t(sequence) * heads, padded = units * run_dim;
         uint16_t *scratch = static_cast<uint16_t *>(h3b_workspace(gpu, 4 * padded * sizeof(uint16_t)));
         if (!scratch) return h3b_fail(gpu, "sdpa_f32: cannot allocate the BF16 operands");
         h3_gpu_tensor half[4];
@@ -1458,16 +1480,16 @@ extern "C" int h3_gpu_sdpa_f32(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
         }
         const float *const sources[3] = {h3b_ptr<float>(query), h3b_ptr<float>(key), h3b_ptr<float>(value)};
         uint16_t *const targets[3] = {scratch, scratch + padded, scratch + 2 * padded};
-        h3b_f32_to_bf16_pad3(gpu, sources, targets, units, head_dim, AT_D);
+        h3b_f32_to_bf16_pad3(gpu, sources, targets, units, head_dim, run_dim);
         if (!h3b_launched(gpu, "sdpa_f32 operands")) return 0;
         /* a block-sparse mask registered for the DiT's BF16 attention does not apply here (the
          * reference passes none on this route, h3_cuda_attention.cu:3010) */
         const uint32_t masked_rows = gpu->sparse_rows;
         gpu->sparse_rows = 0;
-        const int ok = sdpa_common(gpu, &half[3], &half[0], &half[1], &half[2], sequence, heads, AT_D, scale, 0);
+        const int ok = sdpa_common(gpu, &half[3], &half[0], &half[1], &half[2], sequence, heads, run_dim, scale, 0);
         gpu->sparse_rows = masked_rows;
         if (!ok) return 0;
-        h3b_bf16_to_f32_unpad(gpu, scratch + 3 * padded, h3b_ptr<float>(output), units, head_dim, AT_D);
+        h3b_bf16_to_f32_unpad(gpu, scratch + 3 * padded, h3b_ptr<float>(output), units, head_dim, run_dim);
         return h3b_launched(gpu, "sdpa_f32 result");
     }
     if (head_dim > uint32_t(kSimtThreads * kSimtMaxDimsPerThread))

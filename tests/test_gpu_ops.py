@@ -314,6 +314,7 @@ def test_qkv_rope(gpu, pkg, seq, heads, hd, half, grouped):
 @pytest.mark.parametrize("seq,heads,hd", [
     (5, 2, 8), (100, 3, 64), (130, 2, 128),      # the reference's own test shapes
     (64, 1, 128), (65, 2, 128), (128, 1, 128), (129, 3, 128), (1000, 4, 128), (1, 1, 128),
+    (1000, 3, 64), (129, 2, 64),                 # head_dim 64 on the one-tile tensor-core kernel
 ])
 @pytest.mark.parametrize("head_major", [0, 1])
 @pytest.mark.parametrize("two_tiles", [False, True])
