@@ -796,7 +796,9 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
  * per cycle = 1,250 of the ~1,850 cycles a step takes; the two-tile kernel shares K and V between
  * its tiles (128 KiB per tile step) but pays the serial chain. All waits are mbarrier waits with
  * the context's budget (no named barriers: a group that gives up can never leave the other one
- * blocked). Dense attention only; the block-sparse mask keeps the two-tile kernel. */
+ * blocked). Dense attention only; the block-sparse mask keeps the two-tile kernel. Template
+ * parameter D: head_dim 128, or 64 (the video-VAE decoder's: tiles of one 64-dim box, four Q.K^T
+ * instructions per step, N = 64 for P.V, local output only). */
 constexpr int A2_QT = 128, A2_KV = 128;
 constexpr int A2_BOX_BYTES = A2_KV * 64 * 2;                /* a TMA box: 128 rows x 64 dims = 16 KiB */
 constexpr int A2_STAGES = 3, A2_S_BUFFERS = 3;
