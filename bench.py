@@ -1038,7 +1038,8 @@ def run_vae_arm(args):
     registers, zero = weight(v["registers"] * v["hidden"], 1.0), weight(v["hidden"], fill=0.0)
     norm_out_w, norm_out_b = weight(v["hidden"], fill=1.0), weight(v["hidden"])
     proj_w, proj_b = weight(v["output_patch"] * v["hidden"]), weight(v["output_patch"])
-    act = {name: mem.f32(n) for name, n in dict(
+    # the library's own tensors, as the reference's host allocates them (h3_video_vae.c:399-423)
+    act = {name: gpu.new(n, pkg.F32) for name, n in dict(
         latent=patches * v["latent"], post=patches * v["latent"], patch_hidden=patches * v["hidden"],
         hidden=rows * v["hidden"], norm=rows * v["hidden"], qkv=rows * inner * 3, query=rows * inner, key=rows * inner,
         value=rows * inner, heads=rows * inner, branch=rows * v["hidden"], ff1=rows * v["ffn"] * 2,
@@ -1107,7 +1108,8 @@ def run_vae_arm(args):
     stats1 = gpu.stats()
     ms = start.elapsed_time(stop) / args.steps
     # end to end: host latent rows in, projected pixels out, every step
-    latent_view, out_view = mem.torch_of(act["latent"]), mem.torch_of(act["projected"])
+    latent_view = mem.torch_of(act["latent"]).view(torch.float32)        # byte views of the library's memory
+    out_view = mem.torch_of(act["projected"]).view(torch.float32)
     sync()
     start.record()
     for _ in range(args.steps):
