@@ -206,6 +206,35 @@ def test_linear_f32_forgets_the_weight_rows_when_the_weight_changes(gpu, pkg):
     assert rel_l2(out.read(), product(w2)) < 5e-4
 
 
+@pytest.mark.parametrize("layer", [False, True])
+def test_norm_rows_left_for_the_projection_equal_converted_rows(gpu, pkg, layer):
+    """A norm leaves its output rows as scaled FP16 beside the F32 result; the projection that
+    follows uses them. The same projection on a fresh copy of the F32 result (converted by the
+    projection itself) must give the same bits."""
+    rows, k, n = 257, 2048, 384
+    x, w, b = nf(rows * k, 40, 3.0), nf(k, 41, 0.1) + 1.0, nf(k, 42)
+    weight, bias = nf(n * k, 43, 1.0 / np.sqrt(k)), nf(n, 44)
+    tx, tw, tb, tweight, tbias = gpu.f32(x), gpu.f32(w), gpu.f32(b), gpu.f32(weight), gpu.f32(bias)
+    normed, out_a, out_b = gpu.new(rows * k, pkg.F32), gpu.new(rows * n, pkg.F32), gpu.new(rows * n, pkg.F32)
+
+    def norm():
+        if layer:
+            gpu.op("layer_norm_f32", normed, tx, tw, tb, rows, k, 1e-5)
+        else:
+            gpu.op("rms_norm_f32", normed, tx, tw, rows, k, 1e-5)
+    run(gpu, lambda: (norm(), gpu.op("linear_f32", out_a, normed, tweight, tbias, rows, k, n)))
+    copy = gpu.f32(normed.read())
+    run(gpu, lambda: gpu.op("linear_f32", out_b, copy, tweight, tbias, rows, k, n))
+    assert np.array_equal(out_a.read().view(np.uint32), out_b.read().view(np.uint32))
+    want = o.layer_norm_f32(x, w, b, rows, k) if layer else o.rms_norm_f32(x, w, rows, k)
+    close(normed.read(), want, 1e-5, 1e-5, what="norm")
+    # writing the normed tensor again drops the rows: the next projection sees the new contents
+    run(gpu, lambda: gpu.op("scale_add_f32", normed, normed, normed, gpu.f32(np.ones(k, np.float32)), rows, k))
+    run(gpu, lambda: gpu.op("linear_f32", out_a, normed, tweight, tbias, rows, k, n))
+    doubled = (2.0 * want.reshape(rows, k).astype(np.float64)) @ weight.reshape(n, k).astype(np.float64).T + bias
+    assert rel_l2(out_a.read(), doubled.reshape(-1)) < 5e-4
+
+
 def decoder_block_weights(seed):
     rng = np.random.default_rng(seed)
 
