@@ -887,14 +887,21 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             mbar_expect_tx(q_full, (1 + first) * A2_TILE_BYTES);
             load(q_smem, &map_q, q_full, q_block * A2_QT);
             for (uint32_t j = 0; j < first; j++) load(k_smem + j * A2_TILE_BYTES, &map_k, q_full, j * A2_KV);
+            /* the V halves of the first three stages are empty from the start: their tiles go out
+             * now (the barrier is told the stage's whole byte count, K(j+3) follows in the loop) */
+            for (uint32_t j = 0; j < first; j++) {
+                mbar_expect_tx(go + 8 * j, (j + 3 < n_steps ? 2 : 1) * A2_TILE_BYTES);
+                load(v_smem + j * A2_TILE_BYTES, &map_v, go + 8 * j, j * A2_KV);
+            }
             for (uint32_t j = 0; j < n_steps; j++) {
                 /* the stage is free once S(j) has been seen: Q.K(j)^T and P(j-3).V(j-3) are done */
                 const uint32_t stage = j % A2_STAGES;
-                if (!mbar_wait(stage_free + 8 * stage, (j / A2_STAGES) & 1u, stop, budget)) break;
                 const bool ahead = j + 3 < n_steps;
-                mbar_expect_tx(go + 8 * stage, (ahead ? 2 : 1) * A2_TILE_BYTES);
+                if (j < 3 && !ahead) continue;            /* nothing left to load for this step */
+                if (!mbar_wait(stage_free + 8 * stage, (j / A2_STAGES) & 1u, stop, budget)) break;
+                if (j >= 3) mbar_expect_tx(go + 8 * stage, (ahead ? 2 : 1) * A2_TILE_BYTES);
                 if (ahead) load(k_smem + stage * A2_TILE_BYTES, &map_k, go + 8 * stage, (j + 3) * A2_KV);
-                load(v_smem + stage * A2_TILE_BYTES, &map_v, go + 8 * stage, j * A2_KV);
+                if (j >= 3) load(v_smem + stage * A2_TILE_BYTES, &map_v, go + 8 * stage, j * A2_KV);
             }
         }
     } else if (warp == 1) {
