@@ -2,10 +2,10 @@
  * attention. Replaces the reference's h3_cuda_attention.cu for the DiT path
  * behind the same C ABI.
  *
- * Flash attention on the 5th-generation tensor cores (head_dim 128), two kernels. Dense calls
- * take h3b_sdpa_tc2 (described at its definition below: one 128-row query tile per CTA, three
- * score buffers, softmax groups alternating over key steps); calls under a block-sparse mask, and
- * dense calls with H3B_SDPA_TWO_TILES=1, take h3b_sdpa_tc:
+ * Flash attention on the 5th-generation tensor cores (head_dim 128), two kernels. Calls take
+ * h3b_sdpa_tc2 (described at its definition below: one 128-row query tile per CTA, three
+ * score buffers, softmax groups alternating over key steps; dense or under a block-sparse
+ * mask); with H3B_SDPA_TWO_TILES=1 they take h3b_sdpa_tc:
  *   grid = (ceil(S/256), heads); one CTA per SM works on two 128-row query tiles that
  *   ping-pong: while one tile's softmax runs, the tensor core works for the other, and every
  *   K/V tile fetched into shared memory is used by both.
@@ -308,8 +308,10 @@ struct AttnArgs {
      * [rows_local][heads_total][128] at head head0 + head */
     uint32_t world, rows_local, heads_total, head0;
     uint16_t *peer_o[8];
-    /* block-sparse mask: per-CTA step lists (see h3_gpu); NULL = dense */
+    /* block-sparse mask: step lists per CTA of two query tiles and per query block (see
+     * h3_gpu); NULL = dense */
     const uint32_t *sparse_cta_ptr, *sparse_steps;
+    const uint32_t *sparse_block_ptr, *sparse_block_steps;
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
@@ -796,7 +798,10 @@ h3b_sdpa_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
  * per cycle = 1,250 of the ~1,850 cycles a step takes; the two-tile kernel shares K and V between
  * its tiles (128 KiB per tile step) but pays the serial chain. All waits are mbarrier waits with
  * the context's budget (no named barriers: a group that gives up can never leave the other one
- * blocked). Dense attention only; the block-sparse mask keeps the two-tile kernel. Template
+ * blocked). Under a block-sparse mask (SPARSE) the key steps are the query block's own list of
+ * 128-key tiles instead of all tiles in order, and a 64-key half the block does not attend gets
+ * -inf scores; a block that lists nothing runs one step with both halves off and stores zeros.
+ * With one query tile per CTA no step is spent on tiles only the neighbouring block lists. Template
  * parameter D: head_dim 128, or 64 (the video-VAE decoder's: tiles of one 64-dim box, four Q.K^T
  * instructions per step, N = 64 for P.V, local output only). */
 constexpr int A2_QT = 128, A2_KV = 128;
@@ -813,7 +818,7 @@ constexpr size_t a2_smem() { return size_t(1 + 2 * A2_STAGES) * a2_tile_bytes<D>
 static_assert(a2_smem<128>() <= 232448, "the step-alternating attention kernel needs at most 227 KiB of shared memory");
 constexpr uint32_t A2_COL_S = 0, A2_COL_O = A2_S_BUFFERS * A2_KV;
 
-template <bool PUSH, int D>
+template <bool PUSH, int D, bool SPARSE = false>
 __global__ void __launch_bounds__(A2_THREADS, 1)
 h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
              const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
@@ -825,7 +830,7 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     const uint32_t k_smem = q_smem + A2_TILE_BYTES;
     const uint32_t v_smem = k_smem + A2_STAGES * A2_TILE_BYTES;
     const uint32_t bars = v_smem + A2_STAGES * A2_TILE_BYTES;
-    const uint32_t q_full = bars;                              /* 1                    */
+    const uint32_t q_full = bars;                              /* 1: Q and K(0)        */
     const uint32_t go = q_full + 8;                            /* [stage] = 3: tiles loaded and P published */
     const uint32_t stage_free = go + 8 * A2_STAGES;            /* [stage] = 3          */
     const uint32_t s_full = stage_free + 8 * A2_STAGES;        /* [buffer] = 3         */
@@ -834,7 +839,8 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     const uint32_t o_done = ref_bar + 64;                      /* 1                    */
     const uint32_t sum_bar = o_done + 8;                       /* [quarter] = 4        */
     const uint32_t out_bar = sum_bar + 32;                     /* [quarter] = 4        */
-    const uint32_t tmem_holder = out_bar + 32;
+    const uint32_t k_first = out_bar + 32;                     /* [2]: K(1), K(2) of the prologue */
+    const uint32_t tmem_holder = k_first + 16;
     volatile int *stop = reinterpret_cast<volatile int *>(at_smem + (tmem_holder + 8 - base));
     float *state = reinterpret_cast<float *>(at_smem + (bars - base) + A2_BAR_BYTES);
     float *row_reference = state;                              /* [128]: reference maximum (log2 units) */
@@ -843,13 +849,28 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_block = blockIdx.x, head = blockIdx.y;
-    const uint32_t n_steps = (args.seq + A2_KV - 1) / A2_KV;
+    /* dense: key tiles 0 .. n_steps-1 in order; under a block-sparse mask this query block's
+     * step list (at least one step, never more than the dense count) */
+    uint32_t n_steps = (args.seq + A2_KV - 1) / A2_KV;
+    const uint32_t *steps = nullptr;
+    if (SPARSE) {
+        const uint32_t first = args.sparse_block_ptr[q_block];
+        steps = args.sparse_block_steps + first;
+        n_steps = min(n_steps, args.sparse_block_ptr[q_block + 1] - first);
+    }
     const long long budget = args.wait_cycles;
 
     if ((base & 1023u) != 0) {  /* swizzled tiles need 1024-byte alignment */
         if (threadIdx.x == 0) atomicMax(args.status, int(H3B_STATUS_ATTN_TIMEOUT));
         return;
     }
+    /* one K, V or Q tile (two 64-dim boxes for head_dim 128) */
+    auto load = [&](uint32_t smem, const CUtensorMap *map, uint32_t bar, uint32_t row) {
+        tma_load_3d(smem, map, bar, 0, int(head), int(row));
+        if (D == 128) tma_load_3d(smem + A2_BOX_BYTES, map, bar, 64, int(head), int(row));
+    };
+    /* first key row of step j */
+    auto key_row = [&](uint32_t j) { return (SPARSE ? (steps[j] & 0x0fffffffu) : j) * A2_KV; };
     if (threadIdx.x == 0) {
         *stop = 0;
         mbar_init(q_full, 1);
@@ -863,10 +884,30 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         }
         mbar_init(o_done, 1);
         for (int q = 0; q < 4; q++) { mbar_init(sum_bar + 8 * q, 2); mbar_init(out_bar + 8 * q, 2); }
+        mbar_init(k_first, 1);
+        mbar_init(k_first + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        /* The prologue's loads go out here, before the block-wide barrier, so that their latency
+         * runs beside the tensor-memory allocation: the thread that initialised the barriers may
+         * use them at once. Q.K(0)^T starts as soon as Q and K(0) are there; K(1) and K(2) have
+         * barriers of their own. The V halves of the first three stages are empty from the
+         * start: their tiles go out now too (the stage's barrier is told its whole byte count,
+         * K(j+3) follows in the producer's loop). */
+        const uint32_t first = n_steps < 3 ? n_steps : 3;
+        mbar_expect_tx(q_full, 2 * A2_TILE_BYTES);
+        load(q_smem, &map_q, q_full, q_block * A2_QT);
+        load(k_smem, &map_k, q_full, key_row(0));
+        for (uint32_t j = 1; j < first; j++) {
+            mbar_expect_tx(k_first + 8 * (j - 1), A2_TILE_BYTES);
+            load(k_smem + j * A2_TILE_BYTES, &map_k, k_first + 8 * (j - 1), key_row(j));
+        }
+        for (uint32_t j = 0; j < first; j++) {
+            mbar_expect_tx(go + 8 * j, (j + 3 < n_steps ? 2 : 1) * A2_TILE_BYTES);
+            load(v_smem + j * A2_TILE_BYTES, &map_v, go + 8 * j, key_row(j));
+        }
     }
     if (threadIdx.x < A2_QT) row_reference[threadIdx.x] = -INFINITY;
     if (warp == 1) tmem_alloc(tmem_holder, AT_TMEM_COLS);
@@ -879,20 +920,6 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     if (warp == 0) {
         /* ------------------------------------------------ TMA producer */
         if (lane == 0) {
-            auto load = [&](uint32_t smem, const CUtensorMap *map, uint32_t bar, uint32_t row) {
-                tma_load_3d(smem, map, bar, 0, int(head), int(row));
-                if (D == 128) tma_load_3d(smem + A2_BOX_BYTES, map, bar, 64, int(head), int(row));
-            };
-            const uint32_t first = n_steps < 3 ? n_steps : 3;
-            mbar_expect_tx(q_full, (1 + first) * A2_TILE_BYTES);
-            load(q_smem, &map_q, q_full, q_block * A2_QT);
-            for (uint32_t j = 0; j < first; j++) load(k_smem + j * A2_TILE_BYTES, &map_k, q_full, j * A2_KV);
-            /* the V halves of the first three stages are empty from the start: their tiles go out
-             * now (the barrier is told the stage's whole byte count, K(j+3) follows in the loop) */
-            for (uint32_t j = 0; j < first; j++) {
-                mbar_expect_tx(go + 8 * j, (j + 3 < n_steps ? 2 : 1) * A2_TILE_BYTES);
-                load(v_smem + j * A2_TILE_BYTES, &map_v, go + 8 * j, j * A2_KV);
-            }
             for (uint32_t j = 0; j < n_steps; j++) {
                 /* the stage is free once S(j) has been seen: Q.K(j)^T and P(j-3).V(j-3) are done */
                 const uint32_t stage = j % A2_STAGES;
@@ -900,8 +927,8 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
                 if (j < 3 && !ahead) continue;            /* nothing left to load for this step */
                 if (!mbar_wait(stage_free + 8 * stage, (j / A2_STAGES) & 1u, stop, budget)) break;
                 if (j >= 3) mbar_expect_tx(go + 8 * stage, (ahead ? 2 : 1) * A2_TILE_BYTES);
-                if (ahead) load(k_smem + stage * A2_TILE_BYTES, &map_k, go + 8 * stage, (j + 3) * A2_KV);
-                if (j >= 3) load(v_smem + stage * A2_TILE_BYTES, &map_v, go + 8 * stage, j * A2_KV);
+                if (ahead) load(k_smem + stage * A2_TILE_BYTES, &map_k, go + 8 * stage, key_row(j + 3));
+                if (j >= 3) load(v_smem + stage * A2_TILE_BYTES, &map_v, go + 8 * stage, key_row(j));
             }
         }
     } else if (warp == 1) {
@@ -936,7 +963,14 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         bool alive = __all_sync(0xffffffffu, mbar_wait(q_full, 0, stop, budget));
         if (alive) {
             tc_fence_after();
-            for (uint32_t j = 0; j < 3 && j < n_steps; j++) issue_qk(j);
+            issue_qk(0);
+        }
+        for (uint32_t j = 1; alive && j < 3 && j < n_steps; j++) {
+            alive = __all_sync(0xffffffffu, mbar_wait(k_first + 8 * (j - 1), 0, stop, budget));
+            if (alive) {
+                tc_fence_after();
+                issue_qk(j);
+            }
         }
         /* has the barrier of the coming step been seen complete? */
         uint32_t ready = 0;
@@ -1007,6 +1041,9 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         for (uint32_t j = group; alive && j < n_steps; j += 2) {
             const uint32_t buffer = j % A2_S_BUFFERS, round = (j / A2_S_BUFFERS) & 1u;
             const uint32_t tmem_s = tmem_base + A2_COL_S + buffer * A2_KV + lane_base;   /* also P */
+            /* key tile of this step and which of its 64-key halves the query block attends
+             * (read before the wait, which hides the load) */
+            const uint32_t step_word = SPARSE ? steps[j] : (j | 0x30000000u);
             alive = __all_sync(0xffffffffu, mbar_wait(s_full + 8 * buffer, round, stop, budget));
             if (!alive) break;
             tc_fence_after();
@@ -1021,11 +1058,21 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             tmem_ld32(tmem_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
             tmem_ld32(tmem_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
             tmem_ld_wait();
-            const uint32_t valid = args.seq - j * A2_KV;
+            const uint32_t valid = args.seq - (step_word & 0x0fffffffu) * A2_KV;
             if (valid < uint32_t(A2_KV)) {
 #pragma unroll
                 for (int i = 0; i < 128; i++)
                     if (uint32_t(i) >= valid) s[i] = 0xff800000u;        /* -inf */
+            }
+            if (SPARSE) {
+                if (!(step_word & 0x10000000u)) {
+#pragma unroll
+                    for (int i = 0; i < 64; i++) s[i] = 0xff800000u;
+                }
+                if (!(step_word & 0x20000000u)) {
+#pragma unroll
+                    for (int i = 64; i < 128; i++) s[i] = 0xff800000u;
+                }
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -1078,7 +1125,9 @@ h3b_sdpa_tc2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
                 sum *= reference == -INFINITY ? 0.0f : fast_exp2(reference - row_ref);
                 reference = row_ref;
             }
-            const float neg_m = -row_ref;
+            /* a query block whose list is empty has one step with both halves off: its reference
+             * stays -inf, and the probabilities must come out 0, not exp2(-inf + inf) */
+            const float neg_m = SPARSE && row_ref == -INFINITY ? 0.0f : -row_ref;
             const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
             uint64_t sum_a = 0, sum_b = 0;
 #pragma unroll
@@ -1254,7 +1303,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
                                  h3b_sdpa_tc<true, false>, h3b_sdpa_tc<true, true>})
                 ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 int(AT_SMEM)) == cudaSuccess;
-            for (auto *kernel : {h3b_sdpa_tc2<false, 128>, h3b_sdpa_tc2<true, 128>})
+            for (auto *kernel : {h3b_sdpa_tc2<false, 128, false>, h3b_sdpa_tc2<true, 128, false>,
+                                 h3b_sdpa_tc2<false, 128, true>, h3b_sdpa_tc2<true, 128, true>})
                 ok = ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 int(a2_smem<128>())) == cudaSuccess;
             ok = ok && cudaFuncSetAttribute(h3b_sdpa_tc2<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1266,10 +1316,10 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
             configured = true;
         }
         configure_guard.unlock();
-        /* dense calls take the kernel whose softmax groups alternate over key steps; the
-         * block-sparse mask (and H3B_SDPA_TWO_TILES=1) the one that alternates over two query tiles */
+        /* the kernel whose softmax groups alternate over key steps, unless H3B_SDPA_TWO_TILES=1
+         * asks for the one that alternates over two query tiles */
         const char *pick = getenv("H3B_SDPA_TWO_TILES");
-        const bool step_kernel = !sparse && !(pick && *pick && strcmp(pick, "0") != 0);
+        const bool step_kernel = !(pick && *pick && strcmp(pick, "0") != 0);
         CUtensorMap map_q, map_k, map_v;
         if (!make_qkv_map(&map_q, h3b_ptr<uint16_t>(query), seq, heads, step_kernel ? A2_QT : AT_Q, hd) ||
             !make_qkv_map(&map_k, h3b_ptr<uint16_t>(key), seq, heads, AT_KV, hd) ||
@@ -1288,6 +1338,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
         if (sparse) {
             args.sparse_cta_ptr = gpu->sparse_cta_ptr;
             args.sparse_steps = gpu->sparse_steps;
+            args.sparse_block_ptr = gpu->sparse_block_ptr;
+            args.sparse_block_steps = gpu->sparse_block_steps;
         }
         args.status = gpu->status_device;
         args.wait_cycles = gpu->wait_cycles;
@@ -1301,7 +1353,8 @@ int sdpa_common(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
                 h3b_sdpa_tc2<false, 64><<<grid, A2_THREADS, a2_smem<64>(), gpu->stream>>>(map_q, map_k, map_v, args);
                 return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
             }
-            auto *kernel = peers ? h3b_sdpa_tc2<true, 128> : h3b_sdpa_tc2<false, 128>;
+            auto *kernel = peers ? (sparse ? h3b_sdpa_tc2<true, 128, true> : h3b_sdpa_tc2<true, 128, false>)
+                                 : (sparse ? h3b_sdpa_tc2<false, 128, true> : h3b_sdpa_tc2<false, 128, false>);
             kernel<<<grid, A2_THREADS, a2_smem<128>(), gpu->stream>>>(map_q, map_k, map_v, args);
             return h3b_launched(gpu, "sdpa_bf16", H3B_SDPA);
         }

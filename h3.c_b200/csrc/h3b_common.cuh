@@ -102,6 +102,11 @@ struct h3_gpu {
     uint32_t sparse_rows = 0;
     uint32_t *sparse_cta_ptr = nullptr;   /* device, ctas + 1 offsets */
     uint32_t *sparse_steps = nullptr;     /* device */
+    /* the same mask per 128-row query block, for the kernel with one query tile per CTA: a step
+     * word = key tile index | 2 mask bits << 28, bit h set when the block attends the 64-key
+     * half h of the tile */
+    uint32_t *sparse_block_ptr = nullptr;    /* device, query blocks + 1 offsets */
+    uint32_t *sparse_block_steps = nullptr;  /* device */
 
     char profile_label[128] = {0};
     double profile_mark = 0.0;

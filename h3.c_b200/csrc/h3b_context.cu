@@ -295,6 +295,15 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     return gpu;
 }
 
+static void sparse_clear(h3_gpu *gpu) {
+    for (uint32_t **list : {&gpu->sparse_cta_ptr, &gpu->sparse_steps, &gpu->sparse_block_ptr,
+                            &gpu->sparse_block_steps}) {
+        if (*list) cudaFree(*list);
+        *list = nullptr;
+    }
+    gpu->sparse_rows = 0;
+}
+
 extern "C" void h3_gpu_free(h3_gpu *gpu) {
     if (!gpu) return;
     cudaSetDevice(gpu->device);
@@ -312,8 +321,7 @@ extern "C" void h3_gpu_free(h3_gpu *gpu) {
         delete gpu->op_profile;
     }
     if (gpu->status_device) cudaFree(gpu->status_device);
-    if (gpu->sparse_cta_ptr) cudaFree(gpu->sparse_cta_ptr);
-    if (gpu->sparse_steps) cudaFree(gpu->sparse_steps);
+    sparse_clear(gpu);
     delete gpu;
 }
 
@@ -425,18 +433,13 @@ extern "C" void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase) {
     gpu->profile_mark = now;
 }
 
-static void sparse_clear(h3_gpu *gpu) {
-    if (gpu->sparse_cta_ptr) cudaFree(gpu->sparse_cta_ptr);
-    if (gpu->sparse_steps) cudaFree(gpu->sparse_steps);
-    gpu->sparse_cta_ptr = gpu->sparse_steps = nullptr;
-    gpu->sparse_rows = 0;
-}
 
 /* Register / clear the block-sparse mask (reference h3_cuda_attention.cu:1812-1857: same
  * validation, same "applies to calls whose row count equals rows"). The CSR over 64-key tiles
- * per 128-row query block is regrouped on the host into per-CTA step lists over 128-key tiles
- * (see h3_gpu in h3b_common.cuh): the union of the two query blocks' lists, ascending, with
- * the per-(query block, 64-key half) bits. A tile listed twice for a block counts once (the
+ * per 128-row query block is regrouped on the host into step lists over 128-key tiles (see
+ * h3_gpu in h3b_common.cuh), ascending: one list per query block with a bit per 64-key half,
+ * and, for the kernel with two query tiles per CTA, the union of the two blocks' lists with
+ * the per-(query block, half) bits. A tile listed twice for a block counts once (the
  * reference kernel would visit it twice; its own mask builder lists each tile once). */
 extern "C" int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t ptr_count,
                                       const uint32_t *idx, size_t idx_count, uint32_t rows) {
@@ -468,10 +471,24 @@ extern "C" int h3_gpu_sdpa_set_sparse(h3_gpu *gpu, const uint32_t *ptr, size_t p
         if (steps.size() == cta_ptr[c]) steps.push_back(0);   /* nothing listed: one all-masked step */
         cta_ptr[c + 1] = uint32_t(steps.size());
     }
-    if (cudaMalloc(reinterpret_cast<void **>(&gpu->sparse_cta_ptr), cta_ptr.size() * 4) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void **>(&gpu->sparse_steps), steps.size() * 4) != cudaSuccess ||
-        cudaMemcpy(gpu->sparse_cta_ptr, cta_ptr.data(), cta_ptr.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
-        cudaMemcpy(gpu->sparse_steps, steps.data(), steps.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+    /* the same per 128-row query block (one query tile per CTA): two bits per step */
+    std::vector<uint32_t> block_ptr(query_blocks + 1, 0), block_steps;
+    for (uint32_t block = 0; block < query_blocks; block++) {
+        std::fill(bits.begin(), bits.end(), uint8_t(0));
+        if (block < listed_blocks)
+            for (uint32_t e = ptr[block]; e < ptr[block + 1]; e++)
+                bits[idx[e] >> 1] |= uint8_t(1u << (idx[e] & 1u));
+        for (uint32_t k = 0; k < key_tiles128; k++)
+            if (bits[k]) block_steps.push_back(k | (uint32_t(bits[k]) << 28));
+        if (block_steps.size() == block_ptr[block]) block_steps.push_back(0);   /* one all-masked step */
+        block_ptr[block + 1] = uint32_t(block_steps.size());
+    }
+    auto upload = [](uint32_t **device, const std::vector<uint32_t> &host) {
+        return cudaMalloc(reinterpret_cast<void **>(device), host.size() * 4) == cudaSuccess &&
+               cudaMemcpy(*device, host.data(), host.size() * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+    };
+    if (!upload(&gpu->sparse_cta_ptr, cta_ptr) || !upload(&gpu->sparse_steps, steps) ||
+        !upload(&gpu->sparse_block_ptr, block_ptr) || !upload(&gpu->sparse_block_steps, block_steps)) {
         cudaGetLastError();
         sparse_clear(gpu);
         return h3b_fail(gpu, "cannot upload the block-sparse attention mask");

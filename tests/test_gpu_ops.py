@@ -320,8 +320,8 @@ def test_qkv_rope(gpu, pkg, seq, heads, hd, half, grouped):
 @pytest.mark.parametrize("two_tiles", [False, True])
 def test_sdpa(gpu, pkg, monkeypatch, seq, heads, hd, head_major, two_tiles):
     """Dense attention on both tensor-core kernels: the default (one query tile per CTA, softmax
-    groups alternating over key steps) and the one the block-sparse mask uses (two query tiles in
-    ping-pong), which H3B_SDPA_TWO_TILES=1 selects for dense calls too."""
+    groups alternating over key steps) and the one with two query tiles in ping-pong, which
+    H3B_SDPA_TWO_TILES=1 selects."""
     if two_tiles:
         if hd != 128:
             pytest.skip("head_dim != 128 takes the SIMT kernel either way")
