@@ -315,6 +315,7 @@ def test_qkv_rope(gpu, pkg, seq, heads, hd, half, grouped):
     (5, 2, 8), (100, 3, 64), (130, 2, 128),      # the reference's own test shapes
     (64, 1, 128), (65, 2, 128), (128, 1, 128), (129, 3, 128), (1000, 4, 128), (1, 1, 128),
     (1000, 3, 64), (129, 2, 64),                 # head_dim 64 on the one-tile tensor-core kernel
+    (1000, 20, 128), (520, 64, 128), (1100, 40, 64),   # more (query block, head) tiles than SMs
 ])
 @pytest.mark.parametrize("head_major", [0, 1])
 @pytest.mark.parametrize("two_tiles", [False, True])
