@@ -1208,9 +1208,12 @@ def vae_reference_cuda_ops(pkg, rows):
     return out
 
 
-def run_sdpa_only(pkg, rows, heads):
-    """Three launches of the dense attention kernel on its own: a case small enough for a
-    multi-section profiler capture (rows x heads x 128 x 3 inputs; 6400,12 holds 118 MB)."""
+def run_sdpa_only(pkg, rows, heads, window=0, timed=0):
+    """The attention kernel on its own: three launches (a case small enough for a multi-section
+    profiler capture: rows x heads x 128 x 3 inputs; 6400,12 holds 118 MB), then `timed` more
+    between CUDA events. window > 0 registers a block-sparse mask first: every 128-row query
+    block lists the 64-key tiles within `window` tiles of its own first one."""
+    import numpy as np
     import torch
     gpu = pkg.Gpu(0)
     count = rows * heads * 128
@@ -1218,11 +1221,34 @@ def run_sdpa_only(pkg, rows, heads):
     tensors = [torch.randn(count, device="cuda", dtype=torch.bfloat16, generator=generator) for _ in range(3)]
     tensors.append(torch.empty(count, device="cuda", dtype=torch.bfloat16))
     q, k, v, out = [gpu.wrap(t.data_ptr(), count, pkg.BF16) for t in tensors]
+    density = 1.0
+    if window > 0:
+        blocks, tiles = (rows + 127) // 128, (rows + 63) // 64
+        lists = [[t for t in range(tiles) if abs(t - 2 * b) <= window] for b in range(blocks)]
+        ptr = np.concatenate([[0], np.cumsum([len(l) for l in lists])]).astype(np.uint32)
+        idx = np.concatenate([np.asarray(l, np.uint32) for l in lists]).astype(np.uint32)
+        if gpu.lib.h3_gpu_sdpa_set_sparse(gpu.handle, ptr.ctypes.data, ptr.size, idx.ctypes.data, idx.size,
+                                          rows) != 1:
+            raise RuntimeError("h3_gpu_sdpa_set_sparse refused the window mask")
+        density = idx.size / (blocks * tiles)
+    scale = 1.0 / math.sqrt(128)
     for _ in range(3):
         gpu.begin()
-        gpu.op("sdpa_bf16", out, q, k, v, rows, heads, 128, 1.0 / math.sqrt(128))
+        gpu.op("sdpa_bf16", out, q, k, v, rows, heads, 128, scale)
         gpu.submit()
-    print(f"sdpa {rows} x {heads} x 128: mean |out| = {float(tensors[3].float().abs().mean()):.4f}")
+    line = f"sdpa {rows} x {heads} x 128, mask density {density:.2f}: mean |out| = {float(tensors[3].float().abs().mean()):.4f}"
+    if timed > 0:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gpu.begin()
+        start.record()
+        for _ in range(timed):
+            gpu.op("sdpa_bf16", out, q, k, v, rows, heads, 128, scale)
+        stop.record()
+        gpu.submit()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / timed
+        line += f"; {ms:.3f} ms per launch ({4.0 * rows * rows * heads * 128 * density / ms / 1e9:.0f} TFLOP/s of listed tiles)"
+    print(line)
     gpu.close()
 
 
@@ -1246,6 +1272,11 @@ def main():
     ap.add_argument("--sdpa-only", metavar="ROWS,HEADS", default=None,
                     help="profiler target: three dense attention launches (head_dim 128, N(0,1) inputs) "
                          "and nothing else; prints no bench line")
+    ap.add_argument("--sdpa-window", type=int, default=0, metavar="TILES",
+                    help="--sdpa-only under a block-sparse window mask: 64-key tiles kept either side of a "
+                         "query block's own (0 = dense)")
+    ap.add_argument("--sdpa-time", type=int, default=0, metavar="LAUNCHES",
+                    help="--sdpa-only: time this many further launches with CUDA events")
     ap.add_argument("--euler-steps", type=int, default=20, help="c5: Euler steps per denoise")
     ap.add_argument("--guidance", type=float, default=5.0,
                     help="c5: guidance scale (the reference has no guidance pass; harness parameter)")
@@ -1255,7 +1286,7 @@ def main():
     import __graft_entry__ as entry
     pkg = entry.load_package()
     if args.sdpa_only:
-        run_sdpa_only(pkg, *map(int, args.sdpa_only.split(",")))
+        run_sdpa_only(pkg, *map(int, args.sdpa_only.split(",")), window=args.sdpa_window, timed=args.sdpa_time)
         return
     if args.workload == "vae_tile":
         if args.impl == "reference":
