@@ -738,6 +738,7 @@ extern "C" int h3_gpu_adaln_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
      * dot product, h3_cuda_dit.cu:202-204), then the projection. */
     uint16_t *normed = static_cast<uint16_t *>(h3b_workspace(gpu, in_count * sizeof(uint16_t)));
     if (!normed) return h3b_fail(gpu, "cannot allocate the final head scratch");
+    h3b_written(inverse);
     RowArgs a = {};
     a.input = h3b_ptr<uint16_t>(input, input_offset);
     a.norm = h3b_ptr<uint16_t>(norm_weight);

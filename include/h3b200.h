@@ -434,15 +434,20 @@ int h3x_cfg_combine_bf16(h3_gpu *gpu, h3_gpu_tensor *out, const h3_gpu_tensor *c
  * fused = bf16(input . fc1^T) with fc1 = [gate rows | up rows] of hidden_dim each, then
  * output[r][c] = bf16(silu(fused[r][c]) * fused[r][hidden_dim + c]); output is [rows][hidden_dim].
  * Counted as one projection. */
+int h3x_linear_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                           const h3_gpu_tensor *fc1_weight, uint32_t rows, uint32_t input_dim,
+                           uint32_t hidden_dim);
+
 /* Declares that an F32 tensor serves as a projection weight (on != 0) or no longer does (0).
  * h3_gpu_linear_f32 keeps the scaled FP16 rows of such a weight between calls instead of
  * converting it every time; tensors made by h3_gpu_tensor_load_f32 / h3_gpu_tensor_from_f32 are
  * declared so already. Every call of this library that writes the tensor drops the rows; after a
- * write this library cannot see (a wrapped tensor written by its owner) call this with on again. */
+ * write this library cannot see (a wrapped tensor written by its owner) call this with on again.
+ * The F32 norms (h3_gpu_rms_norm_f32, h3_gpu_layer_norm_f32) likewise leave the FP16 rows of their
+ * output beside a tensor this library allocated, for the projection that reads it next; they
+ * are dropped the same way, and H3B_NO_HALF_ROWS=1 switches that off for a host that writes such
+ * tensors through their device pointers. */
 int h3x_tensor_keep_half_rows(h3_gpu_tensor *tensor, int on);
-int h3x_linear_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
-                           const h3_gpu_tensor *fc1_weight, uint32_t rows, uint32_t input_dim,
-                           uint32_t hidden_dim);
 
 /* Final head (adaLN + projection) for callers that must not allocate device memory.
  * No counterpart in the reference: its final head always draws its scratch from a
