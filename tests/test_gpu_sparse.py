@@ -6,7 +6,8 @@
     sequence, lists that differ between neighbouring query blocks and single 64-key halves, with
     each of the two tensor-core kernels;
   * the same mask through the reference's own CUDA backend (oracle/_ref/libh3ref.so);
-  * calls with another row count stay dense."""
+  * calls with another row count stay dense;
+  * the sequence-parallel (push) instances of the kernels with a one-rank peer table."""
 from pathlib import Path
 
 import numpy as np
@@ -183,3 +184,29 @@ def test_masked_attention_matches_reference_cuda_backend(pkg):
         finally:
             gpu.close()
     assert_aggregate_close(out["b200"], out["reference"], "sparse vs reference CUDA backend")
+
+
+@pytest.mark.parametrize("masked", [False, True], ids=["dense", "masked"])
+def test_push_form_with_one_rank_equals_the_local_form(pkg, masked, two_tiles):
+    """h3x_sdpa_push with a one-rank peer table stores every output row into this GPU's own
+    buffer: the kernels' sequence-parallel instances (dense and under a mask) on a single GPU,
+    bit for bit what the local call gives."""
+    seq, heads = 900, 3
+    q, k, v = qkv(seq, heads, 21)
+    gpu = pkg.Gpu(0)
+    try:
+        if masked:
+            assert set_sparse(gpu, *random_mask(seq, np.random.default_rng(4), 0.4), seq) == 1
+        local = run_sdpa(pkg, gpu, q, k, v, seq, heads)
+        tq, tk, tv = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v)
+        out = gpu.new(seq * heads * 128, pkg.BF16)
+        peers = pkg.UlyssesPeers()
+        peers.world, peers.rank, peers.rows_local = 1, 0, seq
+        peers.o[0] = out.pointer
+        gpu.begin()
+        gpu.op("h3x_sdpa_push", peers, tq, tk, tv, seq, heads, 128, SCALE)
+        gpu.submit()
+        pushed = out.read()
+    finally:
+        gpu.close()
+    assert np.array_equal(pushed, local)
