@@ -406,6 +406,28 @@ def test_grouped_qkv_linear_rope(gpu, pkg, monkeypatch, rows, k, heads, unfused)
     assert_gemm_close(tv.read(), v, "v")
 
 
+def test_qkv_push_form_with_one_rank_equals_the_local_form(gpu, pkg):
+    """h3x_grouped_qkv_linear_rope_push with a one-rank peer table stores every head's q/k/v row
+    into this GPU's own gathered buffers, [row][head][128] like the local outputs: the GEMM's
+    sequence-parallel epilogue on a single GPU, bit for bit what the local call gives."""
+    rows, k, heads, hd, half = 300, 5376, 7, 128, 48
+    x, w = bf(rows * k, 1), bf(3 * heads * hd * k, 2, 1.0 / np.sqrt(k))
+    qw, kw = bf(hd, 3, 0.5), bf(hd, 4, 0.5)
+    cos, sin = bf(rows * half, 5), bf(rows * half, 6)
+    n = rows * heads * hd
+    local = [gpu.new(n, pkg.BF16) for _ in range(3)]
+    pushed = [gpu.new(n, pkg.BF16) for _ in range(3)]
+    scratch = gpu.new(3 * n, pkg.BF16)
+    t = [gpu.bf16(a) for a in (x, w, qw, kw, cos, sin)]
+    run(gpu, lambda: gpu.op("grouped_qkv_linear_rope_bf16", *local, scratch, *t, rows, k, heads, hd, half, 1e-5))
+    peers = pkg.UlyssesPeers()
+    peers.world, peers.rank, peers.rows_local = 1, 0, rows
+    peers.q[0], peers.k[0], peers.v[0] = (tensor.pointer for tensor in pushed)
+    run(gpu, lambda: gpu.op("h3x_grouped_qkv_linear_rope_push", peers, *t, rows, k, heads, hd, half, 1e-5))
+    for name, a, b in zip("qkv", pushed, local):
+        assert np.array_equal(a.read(), b.read()), name
+
+
 @pytest.mark.parametrize("kernel", ["pairs", "lone"])
 def test_split_tail_round_of_the_tensor_core_gemm(gpu, pkg, monkeypatch, kernel):
     """Tile counts that leave a partly filled last round: the leftover tiles are split along K
